@@ -1,0 +1,444 @@
+#!/usr/bin/env python
+"""Benchmark of the DDF forward at the ddf_resnet50 stage shapes.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload op|model] [--detail PATH]
+
+One "step" is the whole sweep: 7 stage shapes x {bf16, f16} x {mul, add} = 28
+DDF forward calls at B = 128, k = 3, d = 1 (stride-1 shapes (C,H) = (64,56),
+(128,28), (256,14), (512,7); stride-2 shapes (128,56), (256,28), (512,14)).
+Inputs are seeded synthetic tensors: x ~ relu(N(0,1)), filters ~ N(0,1/9).
+
+Prints ONE JSON line.  `value` is algorithmic GB moved per second over the
+whole step with inputs resident in HBM, the step replayed from a CUDA graph and
+timed with CUDA events; `e2e` is the same sweep through `ddf_host` with pinned
+host buffers (host<->device copies inside the timed region); `roofline`
+describes the kernel instance that takes the largest share of the step;
+`cpu_baseline` is the CPU oracle (a port of the reference's arithmetic: the
+reference has no CPU implementation) on a bounded sample.  With N > 1 every rank
+runs the same sweep on its own GPU (the op shards along the batch with no
+collective) and the value is the aggregate.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [(64, 56, 1), (128, 28, 1), (256, 14, 1), (512, 7, 1), (128, 56, 2), (256, 28, 2), (512, 14, 2)]
+BATCH = 128
+K, D = 3, 1
+L2_BYTES = 126 * 1024 * 1024
+MODEL_CFG = {"ddf_mul_resnet50": (torch.float16, 256), "ddf_add_resnet101": (torch.bfloat16, 512)}
+
+
+def algorithmic_bytes(B, C, H, s, es, k=K):
+    oh = H // s
+    return es * (B * C * H * H + B * C * k * k + B * k * k * oh * oh + B * C * oh * oh)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def make_case(C, H, s, dtype, B, device, seed):
+    g = torch.Generator().manual_seed(seed)
+    oh = H // s
+    x = torch.randn(B, C, H, H, generator=g).relu_().to(dtype)
+    cf = (torch.randn(B, C, K, K, generator=g) / 3).to(dtype)
+    sf = (torch.randn(B, K * K, oh, oh, generator=g) / 3).to(dtype)
+    if device is None:
+        return x, cf, sf
+    return x.to(device), cf.to(device), sf.to(device)
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.idx)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            with open(self.path) as f:
+                for line in f:
+                    p = [q.strip() for q in line.split(",")]
+                    if len(p) < 9:
+                        continue
+                    try:
+                        sm.append(float(p[1])); smax.append(float(p[2]))
+                    except ValueError:
+                        continue
+                    for n, v in zip(names, p[5:9]):
+                        if v.lower().startswith("active"):
+                            reasons.add(n)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        hot = [v for v in sm if v >= 0.5 * max(sm)] if sm else []
+        return {"sm_mhz": statistics.median(hot) if hot else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------ CPU legs
+def cpu_sweep_seconds(sample_batch, threads=None):
+    """Times the float32 CPU oracle over the sweep's 7 shapes x 2 modes at a
+    reduced batch.  Returns (seconds, 2-byte algorithmic bytes, threads used)."""
+    from oracle import ddf_oracle
+    if threads:
+        ddf_oracle.set_threads(threads)
+    used = ddf_oracle.max_threads()
+    total_s, total_b = 0.0, 0
+    for i, (C, H, s) in enumerate(SHAPES):
+        x, cf, sf = make_case(C, H, s, torch.float32, sample_batch, None, 10 + i)
+        for mode in ("mul", "add"):
+            ddf_oracle.forward(x[:1], cf[:1], sf[:1], K, D, s, mode)  # page in
+            t0 = time.perf_counter()
+            ddf_oracle.forward(x, cf, sf, K, D, s, mode)
+            total_s += time.perf_counter() - t0
+            total_b += algorithmic_bytes(sample_batch, C, H, s, 2)
+    return total_s, total_b, used
+
+
+def run_reference(args, rank, world):
+    """The reference has no CPU implementation of the op (its entry points raise on
+    CPU tensors), so this arm times the CPU oracle -- a port of the reference's
+    arithmetic -- on all host threads, on a bounded sample of the same sweep."""
+    if rank != 0:
+        return
+    sample_batch = 16
+    for _ in range(max(1, args.warmup)):
+        cpu_sweep_seconds(2)
+    secs, nbytes, used = 0.0, 0, 1
+    for _ in range(args.steps):
+        s_, b_, used = cpu_sweep_seconds(sample_batch)
+        secs += s_; nbytes += b_
+    gbs = nbytes / secs / 1e9
+    line = {
+        "impl": "reference", "metric": "ddf_forward_hbm_gbs", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": secs / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 (the CPU port has no 2-byte path; bytes counted at 2 bytes/element)",
+        "data": "synthetic",
+        "config": workload_config(),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": used, "kind": "port",
+                         "sample": f"7 shapes x (mul, add) at B={sample_batch} of {BATCH}, float32, "
+                                   f"{os.cpu_count()} logical CPUs, OpenMP threads={used}"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def workload_config():
+    return {"workload": "configs[1]: DDF forward sweep at ddf_resnet50 stage shapes",
+            "batch": BATCH, "kernel_size": K, "dilation": D,
+            "shapes_C_H_stride": SHAPES, "io_dtypes": ["bf16", "f16"], "combine": ["mul", "add"],
+            "calls_per_step": len(SHAPES) * 4,
+            "l2": "inputs larger than L2: a step touches 0.87 GB of distinct tensors and the "
+                  "two calls that share inputs (mul, add) are 13 calls (>0.4 GB) apart"}
+
+
+# ------------------------------------------------------------------------------ GPU legs
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from ddfnet_b200 import _lib, ddf
+    from ddfnet_b200.host import ddf_host
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    L = _lib.load()
+    peak, peak_kind = peaks()
+
+    # resident inputs, one set per (dtype, shape); outputs preallocated by the op
+    cases = []  # (mode, dtname, C, H, s, x, cf, sf)
+    tensors = {}
+    for dtname, dtype in (("bf16", torch.bfloat16), ("f16", torch.float16)):
+        for i, (C, H, s) in enumerate(SHAPES):
+            tensors[(dtname, C, H, s)] = make_case(C, H, s, dtype, BATCH, dev, 100 + i)
+    for mode in ("mul", "add"):
+        for dtname in ("bf16", "f16"):
+            for (C, H, s) in SHAPES:
+                cases.append((mode, dtname, C, H, s) + tensors[(dtname, C, H, s)])
+    step_bytes = sum(algorithmic_bytes(BATCH, C, H, s, 2) for (_, _, C, H, s, *_r) in cases)
+
+    def step():
+        outs = []
+        for (mode, _dt, _C, _H, s, x, cf, sf) in cases:
+            outs.append(ddf(x, cf, sf, K, D, s, mode))
+        return outs
+
+    with torch.no_grad():
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        # the step as a CUDA graph: 28 launches replayed without host work between them
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(graph):
+            keep = step()
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        torch.cuda.synchronize()
+
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        n0 = L.ddf_b200_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        elapsed_ms = e0.elapsed_time(e1)
+        # graph replays do not pass through the library's host-side counter
+        launches = (L.ddf_b200_launch_count() - n0) + args.steps * len(cases)
+
+        # per-call durations: each call replayed alone from its own graph over rotating
+        # buffer sets larger than L2, timed with CUDA events
+        per_shape = []
+        if rank == 0:
+            for (mode, dtname, C, H, s, x, cf, sf) in cases:
+                nb = algorithmic_bytes(BATCH, C, H, s, 2)
+                nsets = min(24, max(3, (2 * L2_BYTES) // nb + 2))
+                sets = [(x, cf, sf)] + [(x.clone(), cf.clone(), sf.clone()) for _ in range(nsets - 1)]
+                for st in sets:
+                    ddf(*st, K, D, s, mode)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    held = [ddf(*st, K, D, s, mode) for st in sets]
+                for _ in range(3):
+                    g.replay()
+                reps = 5
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(reps):
+                    g.replay()
+                b.record()
+                torch.cuda.synchronize()
+                us = a.elapsed_time(b) * 1e3 / (reps * nsets)
+                per_shape.append({"C": C, "H": H, "stride": s, "dtype": dtname, "combine": mode,
+                                  "us": round(us, 3), "bytes": nb, "gbs": round(nb / us / 1e3, 1),
+                                  "frac": round(nb / us / 1e3 / peak, 4)})
+                del g, held, sets
+        clocks = sampler.stop() if rank == 0 else None
+
+        # end to end through the host-buffer API: pinned inputs up, result down, every call
+        e2e_steps = max(1, min(args.steps, 3))
+        host_sets = {}
+        for dtname, dtype in (("bf16", torch.bfloat16), ("f16", torch.float16)):
+            for i, (C, H, s) in enumerate(SHAPES):
+                x, cf, sf = make_case(C, H, s, dtype, BATCH, None, 100 + i)
+                oh = H // s
+                host_sets[(dtname, C, H, s)] = (x.pin_memory(), cf.pin_memory(), sf.pin_memory(),
+                                                torch.empty(BATCH, C, oh, oh, dtype=dtype, pin_memory=True))
+        h2d = sum(sum(t.numel() * t.element_size() for t in v[:3]) for v in host_sets.values()) * 2
+        d2h = sum(v[3].numel() * v[3].element_size() for v in host_sets.values()) * 2
+
+        def e2e_step():
+            for (mode, dtname, C, H, s, *_r) in cases:
+                hx, hcf, hsf, hout = host_sets[(dtname, C, H, s)]
+                ddf_host(hx, hcf, hsf, K, D, s, mode, out=hout, device=dev)
+
+        e2e_step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        b.record()
+        torch.cuda.synchronize()
+        e2e_ms = max(a.elapsed_time(b), (time.perf_counter() - t0) * 1e3)
+
+    if world > 1:
+        t = torch.tensor([elapsed_ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, e2e_ms = t.tolist()
+    if rank != 0:
+        return
+
+    ms_per_step = elapsed_ms / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+    e2e_value = world * step_bytes / (e2e_ms / e2e_steps * 1e-3) / 1e9
+
+    # dominant kernel instance = largest share of the step
+    dom = max(per_shape, key=lambda r: r["us"])
+    roof = {"bound": "hbm", "kernel": f"stream_kernel fwd C={dom['C']} H={dom['H']} s={dom['stride']} "
+                                      f"{dom['dtype']} {dom['combine']}",
+            "achieved": dom["gbs"], "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+            "frac": round(dom["gbs"] / peak, 4), "frac_of_8000": round(dom["gbs"] / 8000.0, 4),
+            "traffic": None, "us_per_launch": dom["us"], "algorithmic_bytes": dom["bytes"]}
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            tj = json.load(f)
+        key = f"{dom['C']}x{dom['H']}s{dom['stride']}"
+        if key in tj:
+            roof["traffic"] = tj[key]
+
+    cpu = None
+    if world == 1 or True:
+        sample_batch = 16
+        cpu_sweep_seconds(2)
+        secs, nbytes, used = cpu_sweep_seconds(sample_batch)
+        cpu = {"value": round(nbytes / secs / 1e9, 3), "unit": "GB/s", "cores": used, "kind": "port",
+               "sample": f"7 shapes x (mul, add) at B={sample_batch} of {BATCH}, float32 CPU oracle, "
+                         f"{os.cpu_count()} logical CPUs, OpenMP threads={used}, {secs:.2f} s"}
+
+    line = {
+        "metric": "ddf_forward_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16+f16 I/O, f32 arithmetic", "data": "synthetic",
+        "config": workload_config(),
+        "frac_of_measured_peak": round(value / world / peak, 4),
+        "frac_of_8000": round(value / world / 8000.0, 4),
+        "roofline": roof, "cpu_baseline": cpu,
+        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "per_shape": per_shape,
+    }
+    print(json.dumps(line))
+    if args.detail:
+        with open(args.detail, "w") as f:
+            json.dump(line, f, indent=1)
+
+
+def run_model(args, rank, world, local_rank):
+    """Whole-network inference throughput (images/s) of the DDF-ResNet harness,
+    batch-sharded over the ranks; logits are all-gathered once for checking."""
+    import torch.distributed as dist
+    from ddfnet_b200.resnet import MODELS
+    from ddfnet_b200.shard import batch_slice, gather_batch
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    name = args.model
+    dtype, gbatch = MODEL_CFG[name]
+    lo, hi = batch_slice(gbatch, rank, world)
+    torch.manual_seed(0)
+    model = MODELS[name]().to(dev).to(dtype).eval()
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(gbatch, 3, 224, 224, generator=g)[lo:hi].to(dev, dtype)
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            y = model(x)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            y = model(x)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        logits = gather_batch(y.float(), gbatch)
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    if rank == 0:
+        print(json.dumps({
+            "metric": f"{name}_images_per_s", "value": round(gbatch * args.steps / (ms * 1e-3), 1),
+            "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": str(dtype).replace("torch.", ""), "data": "synthetic",
+            "config": {"workload": f"{name} inference, global batch {gbatch}, 224x224, random init",
+                       "per_gpu_batch": hi - lo},
+            "logits_finite": bool(torch.isfinite(logits).all()), "logits_shape": list(logits.shape)}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="op", choices=["op", "model"])
+    ap.add_argument("--model", default="ddf_mul_resnet50", choices=sorted(MODEL_CFG))
+    ap.add_argument("--detail", default=None, help="also write the JSON, indented, to this file")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the op)")
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        if args.workload == "model":
+            run_model(args, rank, world, local_rank)
+        else:
+            run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,13 @@
+"""ddfnet_b200 -- the Decoupled Dynamic Filter (DDF) operator for NVIDIA B200.
+
+``ddf`` is a drop-in for the reference's autograd op; ``DDFPack`` / ``DDFUpPack``
+/ ``FilterNorm`` mirror the modules that call it (reference: ddf/ddf.py).  The
+arithmetic runs in hand-written sm_100a CUDA kernels behind the C ABI declared
+in include/ddf_b200.h.
+"""
+from .op import DDFFunction, ddf
+from .modules import (DDFPack, DDFUpPack, FilterNorm, build_channel_branch,
+                      build_spatial_branch)
+
+__all__ = ["ddf", "DDFFunction", "DDFPack", "DDFUpPack", "FilterNorm",
+           "build_spatial_branch", "build_channel_branch"]

@@ -1,0 +1,76 @@
+"""ctypes binding of libddf_b200.so (the C ABI declared in include/ddf_b200.h).
+
+There is no CPU implementation and no fallback: if the library is missing,
+``load()`` raises with the command that builds it.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+_lock = threading.Lock()
+_lib = None
+
+F32, F16, BF16, F64 = 0, 1, 2, 3
+MUL, ADD = 0, 1
+VARIANT_AUTO, VARIANT_GENERIC, VARIANT_STREAM = 0, 1, 2
+
+# every symbol include/ddf_b200.h declares
+SYMBOLS = (
+    "ddf_b200_version", "ddf_b200_strerror", "ddf_b200_forward", "ddf_b200_plan",
+    "ddf_b200_backward_workspace", "ddf_b200_backward", "ddf_b200_take_fault",
+    "ddf_b200_launch_count",
+)
+
+
+def library_path() -> str:
+    """Path of the shared library; DDF_B200_LIB overrides it (A/B builds)."""
+    return os.environ.get("DDF_B200_LIB") or os.path.join(_PKG, "libddf_b200.so")
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = library_path()
+        if not os.path.exists(path):
+            raise RuntimeError(
+                f"{path} not found. The DDF op has no CPU or PyTorch fallback; build the CUDA "
+                "library first:  python -m ddfnet_b200.csrc.build")
+        L = ctypes.CDLL(path)
+        i, vp, sz = ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t
+        L.ddf_b200_version.restype = i
+        L.ddf_b200_version.argtypes = []
+        L.ddf_b200_strerror.restype = ctypes.c_char_p
+        L.ddf_b200_strerror.argtypes = [i]
+        L.ddf_b200_forward.restype = i
+        L.ddf_b200_forward.argtypes = [vp] * 4 + [i] * 10 + [vp]
+        L.ddf_b200_plan.restype = i
+        L.ddf_b200_plan.argtypes = [i] * 10
+        L.ddf_b200_backward_workspace.restype = sz
+        L.ddf_b200_backward_workspace.argtypes = [i] * 10
+        L.ddf_b200_backward.restype = i
+        L.ddf_b200_backward.argtypes = [vp] * 7 + [vp, sz] + [i] * 10 + [vp]
+        L.ddf_b200_take_fault.restype = i
+        L.ddf_b200_take_fault.argtypes = []
+        L.ddf_b200_launch_count.restype = ctypes.c_ulonglong
+        L.ddf_b200_launch_count.argtypes = []
+        _lib = L
+        return L
+
+
+class DDFError(RuntimeError):
+    """A non-zero status from libddf_b200.so."""
+
+    def __init__(self, status: int):
+        self.status = status
+        msg = load().ddf_b200_strerror(status)
+        super().__init__(f"{msg.decode() if msg else 'ddf_b200 error'} (status {status})")
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise DDFError(status)

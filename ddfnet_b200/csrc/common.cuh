@@ -1,0 +1,201 @@
+// Shared definitions for the DDF kernels: element-type traits, the problem
+// descriptor passed from the C ABI to the launchers, and thin PTX wrappers
+// (mbarrier, bulk async copy, packed f32x2 arithmetic) for sm_100a.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ddf_b200.h"
+
+namespace ddf {
+
+// ------------------------------------------------------------------ problem descriptor
+struct Problem {
+    int B, C, H, W;    // input (for the backward: the shape of x / gx)
+    int OH, OW;        // H / s, W / s
+    int k, d, s;
+    int combine;       // DDF_B200_MUL / DDF_B200_ADD
+    int dtype;         // DDF_B200_F32 ...
+};
+
+// Status used internally by launchers that may decline a problem.
+constexpr int kNotHandled = 1 << 30;
+
+// ------------------------------------------------------------------ element traits
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    using acc_t = float;
+    static __device__ __forceinline__ float load(const float* p) { return __ldg(p); }
+    static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+};
+template <> struct Elem<double> {
+    using acc_t = double;
+    static __device__ __forceinline__ double load(const double* p) { return __ldg(p); }
+    static __device__ __forceinline__ void store(double* p, double v) { *p = v; }
+};
+template <> struct Elem<__half> {
+    using acc_t = float;
+    static __device__ __forceinline__ float load(const __half* p) {
+        return __half2float(__ldg(p));
+    }
+    static __device__ __forceinline__ void store(__half* p, float v) { *p = __float2half_rn(v); }
+};
+template <> struct Elem<__nv_bfloat16> {
+    using acc_t = float;
+    static __device__ __forceinline__ float load(const __nv_bfloat16* p) {
+        return __bfloat162float(__ldg(p));
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) {
+        *p = __float2bfloat16_rn(v);
+    }
+};
+
+template <int MODE, typename A>
+__device__ __forceinline__ A combine_w(A cfv, A sfv) {
+    return MODE == DDF_B200_MUL ? cfv * sfv : cfv + sfv;
+}
+
+// ------------------------------------------------------------------ shared-memory PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+// One non-blocking probe: true when the phase with this parity has completed.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the limit ran out (the caller records a
+// fault and leaves); never spins forever.
+constexpr uint32_t kWaitLimit = 1u << 22;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t it = 0; it < kWaitLimit; ++it) {
+        if (mbar_test(bar, parity)) return true;
+    }
+    return false;
+}
+
+// Bulk asynchronous copy global -> shared (TMA, untiled).  dst, src 16-byte
+// aligned, bytes a multiple of 16.  Completion is counted on `bar`.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
+                                         uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+            "r"(dst),
+        "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void lds64(uint32_t a, uint32_t& x, uint32_t& y) {
+    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(x), "=r"(y) : "r"(a));
+}
+__device__ __forceinline__ void lds128(uint32_t a, uint32_t& x, uint32_t& y, uint32_t& z,
+                                       uint32_t& w) {
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(x), "=r"(y), "=r"(z), "=r"(w)
+                 : "r"(a));
+}
+__device__ __forceinline__ float ldsf(uint32_t a) { return __uint_as_float(lds32(a)); }
+__device__ __forceinline__ void sts32(uint32_t a, uint32_t v) {
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
+}
+
+// ------------------------------------------------------------------ packed f32x2
+__device__ __forceinline__ unsigned long long f2_pack(float a, float b) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(unsigned long long v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long f2_fma(unsigned long long a, unsigned long long b,
+                                                     unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ unsigned long long f2_mul(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long f2_add(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+// ------------------------------------------------------------------ raw word <-> float
+// A 32-bit word holds EPW = 4 / sizeof(T) elements; element 0 is the low half.
+template <typename T> struct Word;
+template <> struct Word<float> {
+    static constexpr int EPW = 1;
+    static __device__ __forceinline__ float get(uint32_t w, int) { return __uint_as_float(w); }
+    static __device__ __forceinline__ uint32_t put(float a, float) { return __float_as_uint(a); }
+};
+template <> struct Word<__nv_bfloat16> {
+    static constexpr int EPW = 2;
+    static __device__ __forceinline__ float get(uint32_t w, int e) {
+        return __uint_as_float(e == 0 ? (w << 16) : (w & 0xffff0000u));
+    }
+    static __device__ __forceinline__ uint32_t put(float a, float b) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+};
+template <> struct Word<__half> {
+    static constexpr int EPW = 2;
+    static __device__ __forceinline__ float get(uint32_t w, int e) {
+        __half2 h = *reinterpret_cast<__half2*>(&w);
+        return e == 0 ? __low2float(h) : __high2float(h);
+    }
+    static __device__ __forceinline__ uint32_t put(float a, float b) {
+        __half2 v = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&v);
+    }
+};
+
+// Per-device fault word written by the streaming kernels (see take_fault()).
+enum Fault : int {
+    kFaultNone = 0,
+    kFaultConsumerFull = 1,   // a compute warp gave up waiting for a stage to land
+    kFaultConsumerSf = 2,     // a compute warp gave up waiting for the spatial filter
+    kFaultService = 3,        // the service warp made no progress for the whole limit
+    kFaultDrain = 4,          // copies still in flight when the service warp left
+};
+
+}  // namespace ddf

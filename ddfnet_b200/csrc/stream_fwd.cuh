@@ -1,0 +1,603 @@
+// Plane-streaming DDF kernel for sm_100a (forward, and grad-x at stride 1).
+//
+// Work decomposition.  The (b, c) planes of the input are one contiguous run of
+// B*C planes in memory.  The grid is persistent (one CTA per SM); CTA n owns an
+// equal, contiguous share of that run and streams it through shared memory:
+//
+//   service warp   one elected lane issues untiled bulk async copies (TMA,
+//                  cp.async.bulk) of the next stage -- a few whole planes plus
+//                  their channel filters -- into a ring of shared-memory slots,
+//                  each guarded by a full / empty mbarrier pair, and of the
+//                  spatial filter of the next sample into its own buffer.  The
+//                  same warp converts each landed stage's channel filters to
+//                  float and then raises the stage's `ready` barrier.
+//   compute warps  every thread owns P adjacent output pixels of one plane
+//                  position for the whole kernel.  The k*k spatial-filter values
+//                  of those pixels live in registers (they are the same for all
+//                  channels of a sample) and are re-read only when the run
+//                  crosses into the next sample.  Per plane a thread reads its
+//                  k input rows from shared memory as vectors, forms
+//                  w = cf (.) sf in float, accumulates in float and writes P
+//                  results with one vector store.
+//
+// Zero padding costs nothing in the inner loop: rows outside the plane are
+// redirected to a zeroed shared-memory row by an address select, and the halo
+// words left / right of the plane are ANDed with a per-thread constant mask.
+//
+// Bulk copies must start on 16-byte boundaries.  Plane runs start anywhere, so
+// every copy fetches the 16-byte-aligned superset of the bytes it needs and the
+// readers add the remainder (< 16 bytes) to their shared-memory addresses; the
+// launcher declines (kNotHandled) when a tensor's base or total size is not a
+// multiple of 16 bytes, and the caller then uses the generic kernel.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out records a fault
+// code in global memory and the thread leaves the kernel.
+#pragma once
+
+#include <atomic>
+
+#include "common.cuh"
+
+namespace ddf {
+
+constexpr int kMaxSlots = 16;          // ring depth upper bound
+constexpr int kMaxComputeThreads = 416;  // 13 warps; + 1 service warp = 448 threads
+constexpr int kStreamThreads = kMaxComputeThreads + 32;
+constexpr int kStreamMaxRegs = 144;          // 448 threads x 144 registers fit one SM's 64K
+constexpr uint32_t kSmemBudget = 225 * 1024;
+
+struct StreamPlan {
+    const void* in;   // x for the forward, go for grad-x
+    const void* cf;
+    const void* sf;
+    void* out;
+    int C, H, W, OH, OW;
+    int tasks_per_plane;   // OH*OW / P
+    int groups_per_row;    // OW / P
+    int planes_per_pass;   // NP: planes the compute threads cover at once
+    int passes_per_stage;  // PPS
+    int n_slots;           // ring depth
+    int n_compute_warps;
+    long long total_passes;  // B*C / NP
+    uint32_t plane_bytes;    // H*W*sizeof(T)
+    uint32_t sf_bytes;       // k*k*OH*OW*sizeof(T): one sample's spatial filter
+    uint32_t off_zero, off_cfc, cfc_stride, off_sf, off_stage0, stage_stride, off_rawcf;
+    int* fault;
+};
+
+template <typename T, int K, int D, int S, int P>
+struct Geo {
+    static constexpr int KK = K * K;
+    static constexpr int R = (K - 1) / 2;
+    static constexpr int HALO = R * D;
+    static constexpr int ES = (int)sizeof(T);
+    static constexpr int EPW = 4 / ES;
+    static constexpr int MAINN = P * S;          // elements read as the aligned main vector
+    static constexpr int MAINB = MAINN * ES;
+    static constexpr bool SUBWORD = MAINB < 4;   // only P = 1, S = 1 with 2-byte elements
+    static constexpr int MAINW = SUBWORD ? 1 : MAINB / 4;
+    static constexpr int NCOL = (P - 1) * S + 2 * HALO + 1;  // input columns a thread touches
+    static constexpr int NRE = ((P - 1) * S + HALO + 1 - MAINN) > 0 ? ((P - 1) * S + HALO + 1 - MAINN) : 0;
+    static constexpr int NLW = (HALO + EPW - 1) / EPW;   // halo words left of the main vector
+    static constexpr int NRW = (NRE + EPW - 1) / EPW;    // halo words right of it
+    static constexpr int OUTB = P * ES;
+    static_assert(K == 3 || K == 5, "streaming kernel is instantiated for k = 3, 5");
+    static_assert(HALO <= P * S, "halo must fit in one neighbouring pixel group");
+    static_assert(ES == 2 || ES == 4, "2- and 4-byte element types only");
+};
+
+template <int NB>
+__device__ __forceinline__ void lds_vec(uint32_t a, uint32_t (&w)[NB / 4]) {
+    if constexpr (NB == 4) {
+        w[0] = lds32(a);
+    } else if constexpr (NB == 8) {
+        lds64(a, w[0], w[1]);
+    } else if constexpr (NB == 16) {
+        lds128(a, w[0], w[1], w[2], w[3]);
+    } else {
+        static_assert(NB == 32, "vector width");
+        lds128(a, w[0], w[1], w[2], w[3]);
+        lds128(a + 16, w[4], w[5], w[6], w[7]);
+    }
+}
+
+// One input row of a thread's window, as floats.  rp = shared address of the
+// first main element (input column ox0*S of that row).
+template <typename T, typename G>
+__device__ __forceinline__ void load_row(uint32_t rp, uint32_t lmask, uint32_t rmask,
+                                         float (&xr)[G::NCOL]) {
+    if constexpr (G::SUBWORD) {
+#pragma unroll
+        for (int c = 0; c < G::NCOL; ++c) {
+            const int e = c - G::HALO;
+            uint32_t w = lds16(rp + e * G::ES);
+            if (e < 0) w &= lmask;
+            if (e > 0) w &= rmask;
+            xr[c] = Word<T>::get(w, 0);
+        }
+    } else {
+        uint32_t lw[G::NLW > 0 ? G::NLW : 1];
+        uint32_t mw[G::MAINW];
+        uint32_t rw[G::NRW > 0 ? G::NRW : 1];
+#pragma unroll
+        for (int a = 0; a < G::NLW; ++a) lw[a] = lds32(rp - 4 * (G::NLW - a)) & lmask;
+        lds_vec<G::MAINB>(rp, mw);
+#pragma unroll
+        for (int a = 0; a < G::NRW; ++a) rw[a] = lds32(rp + G::MAINB + 4 * a) & rmask;
+#pragma unroll
+        for (int c = 0; c < G::NCOL; ++c) {
+            const int e = c - G::HALO;
+            if (e < 0) {
+                const int idx = e + G::NLW * G::EPW;
+                xr[c] = Word<T>::get(lw[idx / G::EPW], idx % G::EPW);
+            } else if (e < G::MAINN) {
+                xr[c] = Word<T>::get(mw[e / G::EPW], e % G::EPW);
+            } else {
+                const int idx = e - G::MAINN;
+                xr[c] = Word<T>::get(rw[idx / G::EPW], idx % G::EPW);
+            }
+        }
+    }
+}
+
+template <typename T, int P>
+__device__ __forceinline__ void store_out(T* gp, const float (&acc)[P]) {
+    constexpr int ES = (int)sizeof(T);
+    if constexpr (ES == 4) {
+        if constexpr (P == 1) {
+            *reinterpret_cast<float*>(gp) = acc[0];
+        } else if constexpr (P == 2) {
+            *reinterpret_cast<float2*>(gp) = make_float2(acc[0], acc[1]);
+        } else {
+#pragma unroll
+            for (int v = 0; v < P / 4; ++v)
+                reinterpret_cast<float4*>(gp)[v] =
+                    make_float4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+        }
+    } else {
+        if constexpr (P == 1) {
+            Elem<T>::store(gp, acc[0]);
+        } else if constexpr (P == 2) {
+            *reinterpret_cast<uint32_t*>(gp) = Word<T>::put(acc[0], acc[1]);
+        } else if constexpr (P == 4) {
+            *reinterpret_cast<uint2*>(gp) =
+                make_uint2(Word<T>::put(acc[0], acc[1]), Word<T>::put(acc[2], acc[3]));
+        } else {
+            static_assert(P == 8, "pixels per thread");
+            *reinterpret_cast<uint4*>(gp) =
+                make_uint4(Word<T>::put(acc[0], acc[1]), Word<T>::put(acc[2], acc[3]),
+                           Word<T>::put(acc[4], acc[5]), Word<T>::put(acc[6], acc[7]));
+        }
+    }
+}
+
+__device__ __forceinline__ bool warp_test(uint32_t bar, uint32_t parity, int lane) {
+    int ok = 0;
+    if (lane == 0) ok = mbar_test(bar, parity) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// BWDX = false: out = DDF forward of `in` (= x).
+// BWDX = true : out = grad-x computed from `in` (= go); stride must be 1.
+// PACK        : accumulate with packed f32x2 FMAs (two pixels per instruction).
+template <typename T, int K, int D, int S, int P, int MODE, bool BWDX, bool PACK>
+__global__ void __maxnreg__(kStreamMaxRegs)
+stream_kernel(const __grid_constant__ StreamPlan pl) {
+    using G = Geo<T, K, D, S, P>;
+    constexpr int KK = G::KK;
+    constexpr int ES = G::ES;
+    static_assert(!BWDX || S == 1, "grad-x streaming kernel is stride 1 only");
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const uint32_t sbase = smem_u32(smem_raw);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int NST = pl.n_slots;
+    const int NCW = pl.n_compute_warps;
+    const int NP = pl.planes_per_pass;
+    const int PPS = pl.passes_per_stage;
+
+    const uint32_t bar_sf_full = sbase + 8u * (3 * kMaxSlots);
+    const uint32_t bar_sf_empty = bar_sf_full + 8u;
+#define BAR_FULL(s) (sbase + 8u * (uint32_t)(s))
+#define BAR_EMPTY(s) (sbase + 8u * (uint32_t)(kMaxSlots + (s)))
+#define BAR_READY(s) (sbase + 8u * (uint32_t)(2 * kMaxSlots + (s)))
+#define STAGE_BASE(s) (sbase + pl.off_stage0 + (uint32_t)(s) * pl.stage_stride)
+
+    if (tid == 0) {
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(BAR_FULL(s), 1);
+            mbar_init(BAR_EMPTY(s), (uint32_t)NCW);
+            mbar_init(BAR_READY(s), 1);
+        }
+        mbar_init(bar_sf_full, 1);
+        mbar_init(bar_sf_empty, (uint32_t)NCW);
+        mbar_fence_init();
+    }
+    if (tid < 64) sts32(sbase + pl.off_zero + 4u * tid, 0u);  // 256 zero bytes
+    __syncthreads();
+
+    // This CTA's share of the passes (a pass = NP consecutive planes).
+    const long long pass_lo = (pl.total_passes * (long long)blockIdx.x) / gridDim.x;
+    const long long pass_hi = (pl.total_passes * (long long)(blockIdx.x + 1)) / gridDim.x;
+    const int my_passes = (int)(pass_hi - pass_lo);
+    if (my_passes == 0) return;
+    const int my_stages = (my_passes + PPS - 1) / PPS;
+    const long long plane_lo = pass_lo * NP, plane_hi = pass_hi * NP;
+    const int stage_planes = PPS * NP;
+
+    if (warp == NCW) {
+        // ------------------------------------------------------------- service warp
+        int issue_i = 0, conv_j = 0, seg_k = 0;
+        long long seg_b = plane_lo / pl.C;
+        long long seg_plane = plane_lo;  // first plane of the next sample segment
+        uint32_t idle = 0;
+        bool gave_up = false;
+        while (conv_j < my_stages) {
+            bool progress = false;
+            if (issue_i < my_stages) {
+                const long long st_first = plane_lo + (long long)issue_i * stage_planes;
+                long long st_end = st_first + stage_planes;
+                if (st_end > plane_hi) st_end = plane_hi;
+                // A new sample begins inside this stage: its spatial filter is fetched
+                // as soon as the buffer is free, i.e. once every compute warp has copied
+                // the previous sample's values into registers.  Stage copies never wait
+                // for that (the compute warps need the stage to get that far).
+                const bool want_sf = seg_plane < st_end;
+                const bool free_buf =
+                    want_sf &&
+                    (seg_k == 0 || warp_test(bar_sf_empty, (uint32_t)((seg_k - 1) & 1), lane));
+                if (free_buf) {
+                    if (lane == 0) {
+                        const unsigned long long g0 = (unsigned long long)seg_b * pl.sf_bytes;
+                        const unsigned long long a0 = g0 & ~15ull;
+                        const unsigned long long a1 = (g0 + pl.sf_bytes + 15ull) & ~15ull;
+                        mbar_arrive_expect_tx(bar_sf_full, (uint32_t)(a1 - a0));
+                        bulk_g2s(sbase + pl.off_sf, (const char*)pl.sf + a0, (uint32_t)(a1 - a0),
+                                 bar_sf_full);
+                    }
+                    ++seg_k;
+                    ++seg_b;
+                    seg_plane = seg_b * pl.C;
+                    progress = true;
+                } else {
+                    const int slot = issue_i % NST;
+                    const bool free_slot =
+                        issue_i < NST ||
+                        warp_test(BAR_EMPTY(slot), (uint32_t)((issue_i / NST - 1) & 1), lane);
+                    if (free_slot) {
+                        if (lane == 0) {
+                            const unsigned long long g0 = (unsigned long long)st_first * pl.plane_bytes;
+                            const unsigned long long g1 = (unsigned long long)st_end * pl.plane_bytes;
+                            const unsigned long long a0 = g0 & ~15ull, a1 = (g1 + 15ull) & ~15ull;
+                            const unsigned long long c0 = (unsigned long long)st_first * (KK * ES);
+                            const unsigned long long c1 = (unsigned long long)st_end * (KK * ES);
+                            const unsigned long long ca0 = c0 & ~15ull, ca1 = (c1 + 15ull) & ~15ull;
+                            mbar_arrive_expect_tx(BAR_FULL(slot), (uint32_t)((a1 - a0) + (ca1 - ca0)));
+                            bulk_g2s(STAGE_BASE(slot) + 32u, (const char*)pl.in + a0,
+                                     (uint32_t)(a1 - a0), BAR_FULL(slot));
+                            bulk_g2s(STAGE_BASE(slot) + pl.off_rawcf, (const char*)pl.cf + ca0,
+                                     (uint32_t)(ca1 - ca0), BAR_FULL(slot));
+                        }
+                        ++issue_i;
+                        progress = true;
+                    }
+                }
+            }
+            if (conv_j < issue_i) {
+                const int slot = conv_j % NST;
+                if (warp_test(BAR_FULL(slot), (uint32_t)((conv_j / NST) & 1), lane)) {
+                    // Channel filters of this stage: raw elements -> float.
+                    const long long st_first = plane_lo + (long long)conv_j * stage_planes;
+                    long long st_end = st_first + stage_planes;
+                    if (st_end > plane_hi) st_end = plane_hi;
+                    const int n = (int)(st_end - st_first) * KK;
+                    const uint32_t coff = (uint32_t)(((unsigned long long)st_first * (KK * ES)) & 15ull);
+                    const uint32_t src = STAGE_BASE(slot) + pl.off_rawcf + coff;
+                    const uint32_t dst = sbase + pl.off_cfc + (uint32_t)slot * pl.cfc_stride;
+                    for (int e = lane; e < n; e += 32) {
+                        float v;
+                        if constexpr (ES == 4) v = ldsf(src + 4u * e);
+                        else v = Word<T>::get(lds16(src + 2u * e), 0);
+                        sts32(dst + 4u * e, __float_as_uint(v));
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(BAR_READY(slot));
+                    ++conv_j;
+                    progress = true;
+                }
+            }
+            if (progress) {
+                idle = 0;
+            } else if (++idle > kWaitLimit) {
+                gave_up = true;
+                break;
+            }
+        }
+        if (gave_up) {
+            // Record the fault, then let every copy already issued land (bounded)
+            // before this warp leaves.
+            if (lane == 0) atomicCAS(pl.fault, 0, (int)kFaultService);
+            bool drained = true;
+            for (int j = conv_j; j < issue_i; ++j)
+                drained &= mbar_wait(BAR_FULL(j % NST), (uint32_t)((j / NST) & 1));
+            if (seg_k > 0) drained &= mbar_wait(bar_sf_full, (uint32_t)((seg_k - 1) & 1));
+            if (!drained && lane == 0) atomicExch(pl.fault, (int)kFaultDrain);
+        }
+        return;
+    }
+    if (warp > NCW) return;
+
+    // ----------------------------------------------------------------- compute warps
+    const int TP = pl.tasks_per_plane;
+    int pip = tid / TP;  // plane within the pass
+    int task = tid - pip * TP;
+    const bool active = pip < NP;
+    if (!active) { pip = 0; task = 0; }
+    const int oy = task / pl.groups_per_row;
+    const int ox0 = (task - oy * pl.groups_per_row) * P;
+
+    bool rowok[K];
+    uint32_t rowoff[K];
+#pragma unroll
+    for (int i = 0; i < K; ++i) {
+        const int iy = oy * S + (i - G::R) * D;
+        rowok[i] = iy >= 0 && iy < pl.H;
+        rowoff[i] = (uint32_t)((iy * pl.W + ox0 * S) * ES);
+    }
+    const uint32_t lmask = ox0 > 0 ? 0xffffffffu : 0u;
+    const uint32_t rmask = (ox0 + P < pl.OW) ? 0xffffffffu : 0u;
+    const uint32_t zero_row = sbase + pl.off_zero + 64u;
+
+    float sfr[KK][P];
+#pragma unroll
+    for (int t = 0; t < KK; ++t)
+#pragma unroll
+        for (int pp = 0; pp < P; ++pp) sfr[t][pp] = 0.f;
+
+    long long b = plane_lo / pl.C;
+    int c_in_b = (int)(plane_lo - b * pl.C);
+    bool need_sf = true;
+    int seg = 0;
+    const long long out_plane = (long long)pl.OH * pl.OW;
+    T* outp = reinterpret_cast<T*>(pl.out) + (plane_lo + pip) * out_plane + (long long)oy * pl.OW + ox0;
+    const long long out_step = (long long)NP * out_plane;
+
+    for (int st = 0; st < my_stages; ++st) {
+        const int slot = st % NST;
+        const uint32_t ph = (uint32_t)((st / NST) & 1);
+        if (!mbar_wait(BAR_FULL(slot), ph) || !mbar_wait(BAR_READY(slot), ph)) {
+            atomicCAS(pl.fault, 0, (int)kFaultConsumerFull);
+            return;
+        }
+        const int first_pass = st * PPS;
+        const int npass = (my_passes - first_pass) < PPS ? (my_passes - first_pass) : PPS;
+        const unsigned long long st_first_plane = (unsigned long long)plane_lo + (unsigned long long)first_pass * NP;
+        const uint32_t xoff = (uint32_t)((st_first_plane * pl.plane_bytes) & 15ull);
+        uint32_t plane_s = STAGE_BASE(slot) + 32u + xoff + (uint32_t)pip * pl.plane_bytes;
+        uint32_t cfc_s = sbase + pl.off_cfc + (uint32_t)slot * pl.cfc_stride + (uint32_t)pip * (KK * 4);
+
+        for (int q = 0; q < npass; ++q) {
+            if (need_sf) {
+                if (!mbar_wait(bar_sf_full, (uint32_t)(seg & 1))) {
+                    atomicCAS(pl.fault, 0, (int)kFaultConsumerSf);
+                    return;
+                }
+                const uint32_t sfs =
+                    sbase + pl.off_sf + (uint32_t)(((unsigned long long)b * pl.sf_bytes) & 15ull);
+                if constexpr (!BWDX) {
+#pragma unroll
+                    for (int t = 0; t < KK; ++t) {
+                        const uint32_t a = sfs + (uint32_t)(((t * pl.OH + oy) * pl.OW + ox0) * ES);
+                        if constexpr (G::OUTB < 4) {
+                            sfr[t][0] = Word<T>::get(lds16(a), 0);
+                        } else {
+                            uint32_t w[G::OUTB / 4];
+                            lds_vec<G::OUTB>(a, w);
+#pragma unroll
+                            for (int pp = 0; pp < P; ++pp)
+                                sfr[t][pp] = Word<T>::get(w[pp / G::EPW], pp % G::EPW);
+                        }
+                    }
+                } else {
+                    // grad-x: window tap (i,j) over go pairs with the filter value of
+                    // the mirrored tap taken at the neighbouring pixel it came from.
+#pragma unroll
+                    for (int i = 0; i < K; ++i) {
+#pragma unroll
+                        for (int j = 0; j < K; ++j) {
+                            const int ft = KK - 1 - (i * K + j);
+                            const int yy = oy + (i - G::R) * D;
+#pragma unroll
+                            for (int pp = 0; pp < P; ++pp) {
+                                const int xx = ox0 + pp + (j - G::R) * D;
+                                float v = 0.f;
+                                if (yy >= 0 && yy < pl.OH && xx >= 0 && xx < pl.OW) {
+                                    const uint32_t a = sfs + (uint32_t)(((ft * pl.OH + yy) * pl.OW + xx) * ES);
+                                    if constexpr (ES == 4) v = ldsf(a);
+                                    else v = Word<T>::get(lds16(a), 0);
+                                }
+                                sfr[i * K + j][pp] = v;
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_sf_empty);
+                ++seg;
+                need_sf = false;
+            }
+
+            float cfv[KK];
+#pragma unroll
+            for (int t = 0; t < KK; ++t) cfv[t] = ldsf(cfc_s + 4u * t);
+
+            float acc[P];
+#pragma unroll
+            for (int pp = 0; pp < P; ++pp) acc[pp] = 0.f;
+
+#pragma unroll
+            for (int i = 0; i < K; ++i) {
+                const uint32_t rp = rowok[i] ? (plane_s + rowoff[i]) : zero_row;
+                float xr[G::NCOL];
+                load_row<T, G>(rp, lmask, rmask, xr);
+#pragma unroll
+                for (int j = 0; j < K; ++j) {
+                    const int t = i * K + j;
+                    const float c = cfv[BWDX ? (KK - 1 - t) : t];
+                    if constexpr (PACK && P >= 2) {
+#pragma unroll
+                        for (int q2 = 0; q2 < P / 2; ++q2) {
+                            const float w0 = combine_w<MODE, float>(c, sfr[t][q2]);
+                            const float w1 = combine_w<MODE, float>(c, sfr[t][q2 + P / 2]);
+                            unsigned long long a2 = f2_pack(acc[q2], acc[q2 + P / 2]);
+                            a2 = f2_fma(f2_pack(w0, w1),
+                                        f2_pack(xr[q2 * S + j * D], xr[(q2 + P / 2) * S + j * D]), a2);
+                            f2_unpack(a2, acc[q2], acc[q2 + P / 2]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int pp = 0; pp < P; ++pp)
+                            acc[pp] = fmaf(combine_w<MODE, float>(c, sfr[t][pp]), xr[pp * S + j * D], acc[pp]);
+                    }
+                }
+            }
+            if (active) store_out<T, P>(outp, acc);
+
+            plane_s += (uint32_t)NP * pl.plane_bytes;
+            cfc_s += (uint32_t)NP * (KK * 4);
+            outp += out_step;
+            c_in_b += NP;
+            if (c_in_b >= pl.C) {
+                c_in_b = 0;
+                ++b;
+                need_sf = true;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR_EMPTY(slot));
+    }
+#undef BAR_FULL
+#undef BAR_EMPTY
+#undef BAR_READY
+#undef STAGE_BASE
+}
+
+// ------------------------------------------------------------------------ host side
+struct StreamArgs {
+    const void* in;
+    const void* cf;
+    const void* sf;
+    void* out;
+    Problem p;
+    bool bwdx;
+    int sm_count;
+    int* fault;
+    int P;       // pixels per thread chosen by the dispatcher
+    int device;  // current CUDA device index
+};
+
+inline uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+// Fills the plan; returns false when the problem does not fit this kernel.
+template <typename T, int K, int D, int S, int P>
+bool make_stream_plan(const StreamArgs& a, StreamPlan& pl, uint32_t& smem_bytes, int& grid) {
+    using G = Geo<T, K, D, S, P>;
+    const Problem& p = a.p;
+    // Input / output plane geometry as the kernel sees it.
+    const int H = a.bwdx ? p.OH : p.H, W = a.bwdx ? p.OW : p.W;
+    const int OH = a.bwdx ? p.OH : p.OH, OW = a.bwdx ? p.OW : p.OW;
+    if (a.bwdx && (p.s != 1)) return false;
+    if (OW % P != 0 || W != OW * S) return false;
+    if ((long long)H * W * G::ES > (1ll << 20)) return false;
+    const int TP = OH * OW / P;
+    if (TP < 1 || TP > kMaxComputeThreads) return false;
+    int NP = kMaxComputeThreads / TP;
+    while (NP > 1 && p.C % NP != 0) --NP;
+    const long long planes = (long long)p.B * p.C;
+    const uint32_t plane_bytes = (uint32_t)(H * W * G::ES);
+    const uint32_t sf_bytes = (uint32_t)(G::KK * OH * OW * G::ES);
+    // 16-byte rules of the bulk copies.
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    if (!al16(a.in) || !al16(a.cf) || !al16(a.sf) || !al16(a.out)) return false;
+    if ((planes * plane_bytes) % 16 != 0) return false;
+    if ((planes * G::KK * G::ES) % 16 != 0) return false;
+    if (((long long)p.B * sf_bytes) % 16 != 0) return false;
+
+    int PPS = (int)(16384u / ((uint32_t)NP * plane_bytes));
+    if (PPS < 1) PPS = 1;
+    const long long total_passes = planes / NP;
+    // Do not make stages longer than a CTA's share.
+    const long long share = (total_passes + a.sm_count - 1) / a.sm_count;
+    if (PPS > share) PPS = (int)share;
+    if (PPS < 1) PPS = 1;
+    const int SPL = PPS * NP;
+
+    pl.off_zero = 512;
+    pl.off_cfc = pl.off_zero + 256;
+    pl.cfc_stride = round_up((uint32_t)SPL * G::KK * 4u, 16);
+    const uint32_t x_region = 32u + (uint32_t)SPL * plane_bytes + 16u + 32u;
+    pl.off_rawcf = round_up(x_region, 16);
+    pl.stage_stride = round_up(pl.off_rawcf + (uint32_t)SPL * G::KK * G::ES + 32u, 128);
+    const uint32_t sf_region = round_up(sf_bytes + 32u, 128);
+    int slots = kMaxSlots;
+    for (;; --slots) {
+        if (slots < 2) return false;
+        const uint32_t off_sf = round_up(pl.off_cfc + (uint32_t)slots * pl.cfc_stride, 128);
+        const uint32_t total = off_sf + sf_region + (uint32_t)slots * pl.stage_stride;
+        if (total <= kSmemBudget) {
+            pl.off_sf = off_sf;
+            pl.off_stage0 = off_sf + sf_region;
+            smem_bytes = total;
+            break;
+        }
+    }
+    pl.n_slots = slots;
+    pl.in = a.in; pl.cf = a.cf; pl.sf = a.sf; pl.out = a.out;
+    pl.C = p.C; pl.H = H; pl.W = W; pl.OH = OH; pl.OW = OW;
+    pl.tasks_per_plane = TP;
+    pl.groups_per_row = OW / P;
+    pl.planes_per_pass = NP;
+    pl.passes_per_stage = PPS;
+    pl.n_compute_warps = (NP * TP + 31) / 32;
+    pl.total_passes = total_passes;
+    pl.plane_bytes = plane_bytes;
+    pl.sf_bytes = sf_bytes;
+    pl.fault = a.fault;
+    grid = (int)(total_passes < a.sm_count ? total_passes : a.sm_count);
+    return true;
+}
+
+#ifndef DDF_PACK_F32X2
+#define DDF_PACK_F32X2 1
+#endif
+
+template <typename T, int K, int D, int S, int P, int MODE, bool BWDX>
+int stream_launch(const StreamArgs& a, cudaStream_t stream) {
+    StreamPlan pl;
+    uint32_t smem = 0;
+    int grid = 0;
+    if (!make_stream_plan<T, K, D, S, P>(a, pl, smem, grid)) return kNotHandled;
+    constexpr bool PACK = (DDF_PACK_F32X2 != 0) && sizeof(T) == 2 && P >= 2;
+    auto kern = stream_kernel<T, K, D, S, P, MODE, BWDX, PACK>;
+    // Opt in to the large dynamic shared-memory carve-out once per device and
+    // kernel; steady-state launches (and launches under stream capture) then make
+    // no call besides the launch itself.
+    static std::atomic<unsigned long long> opted_in{0};
+    const unsigned long long bit = 1ull << (a.device & 63);
+    if (!(opted_in.load(std::memory_order_acquire) & bit)) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kSmemBudget);
+        if (e != cudaSuccess) return (int)e;
+        opted_in.fetch_or(bit, std::memory_order_release);
+    }
+    const int threads = (pl.n_compute_warps + 1) * 32;
+    kern<<<grid, threads, smem, stream>>>(pl);
+    return (int)cudaGetLastError();
+}
+
+// Runtime (k, d, s, P, mode, bwdx) -> instantiation.  Defined once per element
+// type in stream_inst_<type>.cu.
+template <typename T>
+int stream_dispatch(const StreamArgs& a, cudaStream_t stream);
+
+}  // namespace ddf

@@ -1,0 +1,3 @@
+// Plane-streaming kernel instantiations for __half elements.
+#define DDF_INST_T __half
+#include "stream_inst.inc"

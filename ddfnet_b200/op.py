@@ -1,0 +1,141 @@
+"""``ddf(features, channel_filter, spatial_filter, kernel_size, dilation, stride,
+kernel_combine, version)`` -- drop-in for the reference autograd op
+(``DDFFunction`` / ``ddf`` in ddf/ddf.py:27-122).
+
+Same positional signature, same assertion checks (ddf/ddf.py:32-65), same
+8-tuple of gradients (ddf/ddf.py:119).  Differences, all deliberate:
+
+* float16 and bfloat16 tensors are computed natively (float accumulation) and
+  the result has the input's type; the reference up-casts float16 to float32
+  (ddf/ddf.py:36-42) and cannot take bfloat16.
+* inputs are saved for the backward when autograd asks for any input gradient
+  (``ctx.needs_input_grad``); the reference tests ``requires_grad`` on its
+  up-cast copies (ddf/ddf.py:88-89), which loses the graph under float16.
+* ``version``: '' picks a kernel automatically, 'o' forces the generic kernel,
+  'f' forces the plane-streaming kernel (the reference's 'o' / 'f' select its
+  generic / tiled forward, ddf/ddf.py:77-84).
+* non-contiguous inputs raise RuntimeError, as the reference's native
+  CHECK_CONTIGUOUS does (ddf/src/cuda/ddf_mul_cuda.cpp:28-40).
+
+The arithmetic runs in hand-written CUDA kernels reached through the C ABI of
+libddf_b200.so; there is no CPU path.
+"""
+from __future__ import annotations
+
+import torch
+from torch.autograd import Function
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.F32, torch.float16: _lib.F16, torch.bfloat16: _lib.BF16,
+           torch.float64: _lib.F64}
+_COMBINE = {"mul": _lib.MUL, "add": _lib.ADD}
+_VARIANT = {"": _lib.VARIANT_AUTO, "o": _lib.VARIANT_GENERIC, "f": _lib.VARIANT_STREAM}
+
+
+def _common_dtype(*tensors):
+    dt = tensors[0].dtype
+    for t in tensors[1:]:
+        dt = torch.promote_types(dt, t.dtype)
+    if dt not in _DTYPES:
+        raise TypeError(f"ddf: unsupported dtype {dt}")
+    return dt
+
+
+def _require_contiguous(t, name):
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous ")
+
+
+class DDFFunction(Function):
+    @staticmethod
+    def forward(ctx, features, channel_filter, spatial_filter,
+                kernel_size=3, dilation=1, stride=1, kernel_combine='mul', version=''):
+        assert features.is_cuda, 'input feature must be a CUDA tensor.'
+        assert channel_filter.is_cuda, 'channel_filter must be a CUDA tensor.'
+        assert spatial_filter.is_cuda, 'spatial_filter must be a CUDA tensor.'
+
+        b, c, h, w = features.size()
+        bc, cc, hc, wc = channel_filter.size()
+        assert bc == b and cc == c, \
+            "channel_filter size {} does not match feature size {}".format(
+                channel_filter.size(), features.size())
+        assert hc == kernel_size and wc == kernel_size, \
+            "channel_filter size {} does not match kernel size {}".format(
+                channel_filter.size(), kernel_size)
+        bs, cs, hs, ws = spatial_filter.size()
+        assert bs == b and hs == h // stride and ws == w // stride, \
+            "spatial_filter size {} does not match feature size {} with stride {}".format(
+                spatial_filter.size(), features.size(), stride)
+        assert cs == kernel_size ** 2, \
+            "spatial_filter size {} does not match kernel size {}".format(
+                spatial_filter.size(), kernel_size)
+        assert (kernel_size - 1) % 2 == 0 and kernel_size >= 1 and dilation >= 1 and stride >= 1
+        assert kernel_combine in {'mul', 'add'}, \
+            'only support mul or add combination, instead of {}'.format(kernel_combine)
+        assert version in _VARIANT, "version must be '', 'o' or 'f'"
+        assert channel_filter.device == features.device and spatial_filter.device == features.device
+
+        ctx.in_dtypes = (features.dtype, channel_filter.dtype, spatial_filter.dtype)
+        dt = _common_dtype(features, channel_filter, spatial_filter)
+        features = features.to(dt)
+        channel_filter = channel_filter.to(dt)
+        spatial_filter = spatial_filter.to(dt)
+        _require_contiguous(features, "features")
+        _require_contiguous(channel_filter, "channel_filter")
+        _require_contiguous(spatial_filter, "spatial_filter")
+
+        ctx.kernel_size = kernel_size
+        ctx.dilation = dilation
+        ctx.stride = stride
+        ctx.op_type = kernel_combine
+        ctx.variant = _VARIANT[version]
+
+        output = torch.empty((b, c, h // stride, w // stride), dtype=dt, device=features.device)
+        lib = _lib.load()
+        with torch.cuda.device(features.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            _lib.check(lib.ddf_b200_forward(
+                features.data_ptr(), channel_filter.data_ptr(), spatial_filter.data_ptr(),
+                output.data_ptr(), b, c, h, w, kernel_size, dilation, stride,
+                _COMBINE[kernel_combine], _DTYPES[dt], ctx.variant, stream))
+        if any(ctx.needs_input_grad[:3]):
+            ctx.save_for_backward(features, channel_filter, spatial_filter)
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        assert grad_output.is_cuda
+        features, channel_filter, spatial_filter = ctx.saved_tensors
+        dt = features.dtype
+        grad_output = grad_output.to(dt).contiguous()
+        b, c, h, w = features.size()
+        k, d, s = ctx.kernel_size, ctx.dilation, ctx.stride
+        need_x, need_cf, need_sf = ctx.needs_input_grad[:3]
+        dev = features.device
+        gx = torch.empty_like(features) if need_x else None
+        gcf = torch.empty_like(channel_filter) if need_cf else None
+        gsf = torch.empty_like(spatial_filter) if need_sf else None
+
+        lib = _lib.load()
+        comb, dtc = _COMBINE[ctx.op_type], _DTYPES[dt]
+        with torch.cuda.device(dev):
+            ws_bytes = int(lib.ddf_b200_backward_workspace(b, c, h, w, k, d, s, comb, dtc, ctx.variant))
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
+            stream = torch.cuda.current_stream().cuda_stream
+            ptr = lambda t: t.data_ptr() if t is not None else None
+            _lib.check(lib.ddf_b200_backward(
+                grad_output.data_ptr(), features.data_ptr(), channel_filter.data_ptr(),
+                spatial_filter.data_ptr(), ptr(gx), ptr(gcf), ptr(gsf), ptr(ws), ws_bytes,
+                b, c, h, w, k, d, s, comb, dtc, ctx.variant, stream))
+        dx, dcf, dsf = ctx.in_dtypes
+        if gx is not None and gx.dtype != dx:
+            gx = gx.to(dx)
+        if gcf is not None and gcf.dtype != dcf:
+            gcf = gcf.to(dcf)
+        if gsf is not None and gsf.dtype != dsf:
+            gsf = gsf.to(dsf)
+        return gx, gcf, gsf, None, None, None, None, None
+
+
+ddf = DDFFunction.apply

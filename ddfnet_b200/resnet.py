@@ -1,0 +1,128 @@
+"""DDF-ResNet measurement harness: bottleneck ResNets whose 3x3 convolution
+(``conv2`` of every block) is a DDFPack, as the reference builds them on top of
+timm (ddf_resnet.py:34-63: ``DDFPack(width, kernel_size=3, stride=stride,
+dilation=first_dilation, se_ratio=0.2, kernel_combine=...)``; layer lists at
+ddf_resnet.py:66-111).  timm is not a dependency here: the surrounding network
+is the standard ImageNet bottleneck layout (7x7/2 stem, 3x3/2 max-pool, stride
+on conv2, 1x1-conv + BN projection shortcuts, global pool + FC), written out in
+plain PyTorch.  Parameter counts match the reference's model table
+(README.md:21-24): 16.8 M for the 50-layer and 28.1 M for the 101-layer net.
+
+Only the ``ddf`` call inside DDFPack reaches the CUDA kernels; this file exists
+to measure whole-network inference throughput with the op in place.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from .modules import DDFPack
+
+
+class DDFBottleneck(nn.Module):
+    expansion = 4
+
+    def __init__(self, inplanes, planes, stride=1, downsample=None, kernel_combine='mul',
+                 se_ratio=0.2):
+        super().__init__()
+        width = planes
+        self.conv1 = nn.Conv2d(inplanes, width, 1, bias=False)
+        self.bn1 = nn.BatchNorm2d(width)
+        self.act1 = nn.ReLU(inplace=True)
+        self.conv2 = DDFPack(width, kernel_size=3, stride=stride, dilation=1,
+                             se_ratio=se_ratio, kernel_combine=kernel_combine)
+        self.bn2 = nn.BatchNorm2d(width)
+        self.act2 = nn.ReLU(inplace=True)
+        self.conv3 = nn.Conv2d(width, planes * self.expansion, 1, bias=False)
+        self.bn3 = nn.BatchNorm2d(planes * self.expansion)
+        self.act3 = nn.ReLU(inplace=True)
+        self.downsample = downsample
+
+    def forward(self, x):
+        shortcut = x
+        x = self.act1(self.bn1(self.conv1(x)))
+        x = self.act2(self.bn2(self.conv2(x)))
+        x = self.bn3(self.conv3(x))
+        if self.downsample is not None:
+            shortcut = self.downsample(shortcut)
+        return self.act3(x + shortcut)
+
+
+class DDFResNet(nn.Module):
+    def __init__(self, layers, kernel_combine='mul', num_classes=1000, se_ratio=0.2):
+        super().__init__()
+        self.inplanes = 64
+        self.conv1 = nn.Conv2d(3, 64, 7, stride=2, padding=3, bias=False)
+        self.bn1 = nn.BatchNorm2d(64)
+        self.act1 = nn.ReLU(inplace=True)
+        self.maxpool = nn.MaxPool2d(3, stride=2, padding=1)
+        self.layer1 = self._make_layer(64, layers[0], 1, kernel_combine, se_ratio)
+        self.layer2 = self._make_layer(128, layers[1], 2, kernel_combine, se_ratio)
+        self.layer3 = self._make_layer(256, layers[2], 2, kernel_combine, se_ratio)
+        self.layer4 = self._make_layer(512, layers[3], 2, kernel_combine, se_ratio)
+        self.global_pool = nn.AdaptiveAvgPool2d(1)
+        self.fc = nn.Linear(512 * DDFBottleneck.expansion, num_classes)
+        self.init_weights()
+
+    def _make_layer(self, planes, blocks, stride, kernel_combine, se_ratio):
+        downsample = None
+        if stride != 1 or self.inplanes != planes * DDFBottleneck.expansion:
+            downsample = nn.Sequential(
+                nn.Conv2d(self.inplanes, planes * DDFBottleneck.expansion, 1, stride=stride, bias=False),
+                nn.BatchNorm2d(planes * DDFBottleneck.expansion))
+        layers = [DDFBottleneck(self.inplanes, planes, stride, downsample, kernel_combine, se_ratio)]
+        self.inplanes = planes * DDFBottleneck.expansion
+        for _ in range(1, blocks):
+            layers.append(DDFBottleneck(self.inplanes, planes, 1, None, kernel_combine, se_ratio))
+        return nn.Sequential(*layers)
+
+    def init_weights(self):
+        """Kaiming-normal (fan_out, relu) convolutions, BN gamma = 1 / beta = 0."""
+        for m in self.modules():
+            if isinstance(m, nn.Conv2d):
+                nn.init.kaiming_normal_(m.weight, mode='fan_out', nonlinearity='relu')
+                if m.bias is not None:
+                    nn.init.zeros_(m.bias)
+            elif isinstance(m, nn.BatchNorm2d):
+                nn.init.ones_(m.weight)
+                nn.init.zeros_(m.bias)
+
+    def forward(self, x):
+        x = self.maxpool(self.act1(self.bn1(self.conv1(x))))
+        x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
+        return self.fc(torch.flatten(self.global_pool(x), 1))
+
+    def ddf_layers(self):
+        """The DDFPack modules in network order."""
+        return [m for m in self.modules() if isinstance(m, DDFPack)]
+
+
+_LAYERS = {50: [3, 4, 6, 3], 101: [3, 4, 23, 3], 152: [3, 8, 36, 3]}
+
+
+def ddf_mul_resnet50(**kw):
+    return DDFResNet(_LAYERS[50], 'mul', **kw)
+
+
+def ddf_mul_resnet101(**kw):
+    return DDFResNet(_LAYERS[101], 'mul', **kw)
+
+
+def ddf_mul_resnet152(**kw):
+    return DDFResNet(_LAYERS[152], 'mul', **kw)
+
+
+def ddf_add_resnet50(**kw):
+    return DDFResNet(_LAYERS[50], 'add', **kw)
+
+
+def ddf_add_resnet101(**kw):
+    return DDFResNet(_LAYERS[101], 'add', **kw)
+
+
+def ddf_add_resnet152(**kw):
+    return DDFResNet(_LAYERS[152], 'add', **kw)
+
+
+MODELS = {f.__name__: f for f in (ddf_mul_resnet50, ddf_mul_resnet101, ddf_mul_resnet152,
+                                  ddf_add_resnet50, ddf_add_resnet101, ddf_add_resnet152)}

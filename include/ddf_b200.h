@@ -1,0 +1,134 @@
+/*
+ * ddf_b200.h -- C ABI of libddf_b200.so: the Decoupled Dynamic Filter (DDF)
+ * operator, forward and backward, 'mul' and 'add' combine modes, as hand-written
+ * sm_100a CUDA kernels.
+ *
+ * The library replaces the native layer of the reference project
+ * (theFoxofSky/ddfnet).  There the native entry points are four pybind11
+ * modules taking at::Tensor; here they are plain C functions taking device
+ * pointers and sizes, so any host (ctypes, cffi, a torch extension, C++) can
+ * bind them.  Each declaration cites the reference interface it replaces.
+ *
+ * Semantics (contiguous NCHW, r = (k-1)/2, OH = H/s, OW = W/s, floor):
+ *   w[b,c,t,y,x]  = cf[b,c,i,j] * sf[b,t,y,x]   (mul)   or   cf + sf   (add),  t = i*k + j
+ *   out[b,c,y,x]  = sum_t x[b,c, y*s + (i-r)*d, x*s + (j-r)*d] * w[b,c,t,y,x]   (zero padding)
+ * and the three gradients of that expression.
+ *
+ * Conventions shared by all calls
+ *   - Every pointer is a DEVICE pointer on the current CUDA device; the caller
+ *     owns all memory.  The library allocates nothing, never synchronises the
+ *     host, never exits the process and never throws: it returns a status.
+ *   - All tensors are contiguous, of the element type `dtype`, shapes as below.
+ *   - Every element of every output is written; outputs need not be zeroed.
+ *   - Work is enqueued on `stream` (a cudaStream_t passed as void*; NULL is the
+ *     legacy default stream).  Calls are asynchronous and re-entrant.
+ *   - Status: 0 = success; negative = the argument check that failed
+ *     (DDF_B200_E_*); positive = a cudaError_t reported by the CUDA runtime.
+ */
+#ifndef DDF_B200_H_
+#define DDF_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+#define DDF_B200_F32 0
+#define DDF_B200_F16 1
+#define DDF_B200_BF16 2
+#define DDF_B200_F64 3
+
+/* combine modes: ddf/ddf.py:64-65 ('mul' | 'add') */
+#define DDF_B200_MUL 0
+#define DDF_B200_ADD 1
+
+/* Kernel choice.  The reference's `version` argument (ddf/ddf.py:77-84) picks
+ * between its generic ('o') and tiled ('f') forward; the same letters map to
+ * GENERIC and STREAM here, '' to AUTO. */
+#define DDF_B200_VARIANT_AUTO 0    /* STREAM where the shape qualifies, else GENERIC */
+#define DDF_B200_VARIANT_GENERIC 1 /* one thread per element; any k, d, s, any type   */
+#define DDF_B200_VARIANT_STREAM 2  /* TMA-fed persistent plane-streaming kernels      */
+
+/* argument-check failures */
+#define DDF_B200_E_NULL (-1)        /* a required pointer is NULL                      */
+#define DDF_B200_E_SHAPE (-2)       /* B, C, H, W < 1 or H/s, W/s < 1                  */
+#define DDF_B200_E_KERNEL (-3)      /* k even or < 1, d < 1, or s < 1 (ddf/ddf.py:63)  */
+#define DDF_B200_E_COMBINE (-4)     /* combine not MUL / ADD                           */
+#define DDF_B200_E_DTYPE (-5)       /* unknown dtype                                   */
+#define DDF_B200_E_VARIANT (-6)     /* unknown variant                                 */
+#define DDF_B200_E_UNSUPPORTED (-7) /* VARIANT_STREAM forced on a shape it cannot do   */
+#define DDF_B200_E_WORKSPACE (-8)   /* workspace NULL or smaller than required         */
+#define DDF_B200_E_TOO_LARGE (-9)   /* an index would not fit the kernels' ranges      */
+#define DDF_B200_E_DEVICE (-10)     /* no usable CUDA device / not an sm_100 device    */
+
+/* Library version: major*10000 + minor*100 + patch. */
+int ddf_b200_version(void);
+
+/* Human-readable text for a status returned by this library (static storage). */
+const char* ddf_b200_strerror(int status);
+
+/*
+ * Forward.  Replaces ddf_mul_forward / ddf_add_forward
+ * (ddf/src/ddf_mul_ext.cpp:21-34, ddf/src/ddf_add_ext.cpp:21-34) and the
+ * forward of the "faster" modules (ddf/src/ddf_mul_faster_ext.cpp:13-26), i.e.
+ * the launchers DDFMulForwardLauncher (ddf/src/cuda/ddf_mul_cuda_kernel.cu:167-196)
+ * and DDFMulFasterForwardLauncher (ddf/src/cuda/ddf_mul_faster_cuda_kernel.cu:165-199).
+ *
+ *   x   (B,C,H,W)   cf (B,C,k,k)   sf (B,k*k,H/s,W/s)   ->   out (B,C,H/s,W/s)
+ */
+int ddf_b200_forward(const void* x, const void* cf, const void* sf, void* out,
+                     int B, int C, int H, int W, int k, int d, int s,
+                     int combine, int dtype, int variant, void* stream);
+
+/* Which variant (GENERIC or STREAM) AUTO resolves to for this problem; pointers
+ * are assumed 16-byte aligned.  `backward` = 0 for the forward, 1 for the backward.
+ * Returns a DDF_B200_VARIANT_* value, or a negative status. */
+int ddf_b200_plan(int B, int C, int H, int W, int k, int d, int s,
+                  int combine, int dtype, int backward);
+
+/*
+ * Bytes of scratch the backward needs for this problem (0 is possible).
+ * The reference makes its caller allocate three zero-filled scratch tensors
+ * (ddf/ddf.py:106-108, resized in ddf/src/cuda/ddf_mul_cuda.cpp:85-87); here the
+ * caller provides one untyped block, 256-byte aligned, which need not be zeroed.
+ */
+size_t ddf_b200_backward_workspace(int B, int C, int H, int W, int k, int d, int s,
+                                   int combine, int dtype, int variant);
+
+/*
+ * Backward.  Replaces ddf_mul_backward / ddf_add_backward
+ * (ddf/src/ddf_mul_ext.cpp:36-55, ddf/src/ddf_add_ext.cpp:36-55), i.e.
+ * DDFMulBackwardLauncher (ddf/src/cuda/ddf_mul_cuda_kernel.cu:423-527) and its
+ * six launches (three transposes + DDFBackward_Feature / _Spatial_Filter /
+ * _Channel_Filter).
+ *
+ *   go (B,C,H/s,W/s) , x , cf , sf   ->   gx like x, gcf like cf, gsf like sf
+ *
+ * Any of gx / gcf / gsf may be NULL: that gradient is then not computed
+ * (the reference always computes all three).
+ */
+int ddf_b200_backward(const void* go, const void* x, const void* cf, const void* sf,
+                      void* gx, void* gcf, void* gsf,
+                      void* workspace, size_t workspace_bytes,
+                      int B, int C, int H, int W, int k, int d, int s,
+                      int combine, int dtype, int variant, void* stream);
+
+/*
+ * Reads and clears the per-device fault word that the streaming kernels set
+ * when one of their bounded waits runs out (they then stop instead of spinning).
+ * Synchronises the device.  0 = no fault recorded; otherwise a positive code
+ * naming the wait that gave up.  Returns a negative status on a CUDA error.
+ * No counterpart in the reference (its kernels have no waits).
+ */
+int ddf_b200_take_fault(void);
+
+/* Number of kernel launches this library has enqueued since it was loaded
+ * (all devices, all threads).  Used by the benchmark to report its launch count. */
+unsigned long long ddf_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DDF_B200_H_ */

@@ -1,0 +1,81 @@
+"""CPU-side checks of the C ABI: the library loads, exports every symbol the
+header declares, and rejects bad arguments with the documented status codes
+before touching a device (no compute calls here)."""
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def L():
+    from ddfnet_b200.csrc import build
+    build.build()
+    from ddfnet_b200 import _lib
+    return _lib.load()
+
+
+def _declared_symbols():
+    with open(os.path.join(ROOT, "include", "ddf_b200.h")) as f:
+        text = f.read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ddf_b200_\w+)\s*\(", text)))
+
+
+def test_header_symbols_exported(L):
+    from ddfnet_b200 import _lib
+    declared = _declared_symbols()
+    assert declared, "no declarations found in include/ddf_b200.h"
+    assert sorted(_lib.SYMBOLS) == declared
+    for name in declared:
+        assert getattr(L, name) is not None
+
+
+def test_header_cites_reference():
+    with open(os.path.join(ROOT, "include", "ddf_b200.h")) as f:
+        text = f.read()
+    for cite in ("ddf/src/ddf_mul_ext.cpp:21-34", "ddf/src/ddf_mul_ext.cpp:36-55",
+                 "ddf/src/cuda/ddf_mul_cuda_kernel.cu:423-527"):
+        assert cite in text
+
+
+def test_version_and_strerror(L):
+    assert L.ddf_b200_version() >= 100
+    assert L.ddf_b200_strerror(0) == b"success"
+    for code in range(-10, 0):
+        assert L.ddf_b200_strerror(code).startswith(b"ddf_b200:")
+
+
+def test_argument_checks(L):
+    fwd = lambda *a: L.ddf_b200_forward(None, None, None, None, *a, None)
+    # B, C, H, W, k, d, s, combine, dtype, variant
+    assert fwd(0, 4, 8, 8, 3, 1, 1, 0, 0, 0) == -2
+    assert fwd(1, 4, 8, 8, 4, 1, 1, 0, 0, 0) == -3   # even kernel (ddf/ddf.py:63)
+    assert fwd(1, 4, 8, 8, 3, 0, 1, 0, 0, 0) == -3
+    assert fwd(1, 4, 8, 8, 3, 1, 0, 0, 0, 0) == -3
+    assert fwd(1, 4, 1, 8, 3, 1, 2, 0, 0, 0) == -2   # H/s == 0
+    assert fwd(1, 4, 8, 8, 3, 1, 1, 2, 0, 0) == -4
+    assert fwd(1, 4, 8, 8, 3, 1, 1, 0, 9, 0) == -5
+    assert fwd(1, 4, 8, 8, 3, 1, 1, 0, 0, 5) == -6
+    assert fwd(1, 4, 8, 8, 3, 1, 1, 0, 0, 0) == -1   # NULL pointers
+    assert L.ddf_b200_backward(None, None, None, None, None, None, None, None, 0,
+                               1, 4, 8, 8, 3, 1, 1, 0, 0, 0, None) == -1
+    assert L.ddf_b200_backward_workspace(1, 4, 8, 8, 4, 1, 1, 0, 0, 0) == 0
+
+
+def test_plan_prefers_streaming_at_benchmark_shapes(L):
+    from ddfnet_b200 import _lib
+    for C, H, s in [(64, 56, 1), (128, 28, 1), (256, 14, 1), (512, 7, 1), (128, 56, 2), (256, 28, 2), (512, 14, 2)]:
+        assert L.ddf_b200_plan(128, C, H, H, 3, 1, s, 0, _lib.BF16, 0) == _lib.VARIANT_STREAM
+    assert L.ddf_b200_plan(2, 3, 9, 11, 7, 1, 1, 0, _lib.F32, 0) == _lib.VARIANT_GENERIC
+    assert L.ddf_b200_plan(128, 64, 56, 56, 3, 1, 1, 0, _lib.F64, 0) == _lib.VARIANT_GENERIC
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    import ddfnet_b200._lib as lib
+    monkeypatch.setenv("DDF_B200_LIB", str(tmp_path / "nope.so"))
+    monkeypatch.setattr(lib, "_lib", None)
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        lib.load()

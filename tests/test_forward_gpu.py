@@ -1,0 +1,184 @@
+"""Forward parity on the GPU: the CUDA kernels (through the public `ddf` op and
+hence the C ABI) against the float64 CPU oracle on identical seeded inputs."""
+import pytest
+import torch
+
+from tests.util import DTYPES, check_close, make_inputs, oracle_forward
+
+pytestmark = pytest.mark.gpu
+
+
+def _lib():
+    from ddfnet_b200 import _lib
+    return _lib
+
+
+def _run(x, cf, sf, k, d, s, m, version=""):
+    from ddfnet_b200 import ddf
+    dev = torch.device("cuda:0")
+    return ddf(x.to(dev), cf.to(dev), sf.to(dev), k, d, s, m, version)
+
+
+def _no_fault():
+    assert _lib().load().ddf_b200_take_fault() == 0
+
+
+# ------------------------------------------------------------------ generic kernel: wide sweep
+GENERIC = []
+for k, d in [(1, 1), (3, 1), (3, 2), (3, 3), (5, 1), (5, 2), (7, 1)]:
+    for s in (1, 2):
+        GENERIC.append((2, 3, 9, 11, k, d, s))
+GENERIC += [(1, 1, 5, 5, 3, 1, 1), (1, 33, 10, 12, 3, 1, 2), (1, 70, 10, 10, 3, 2, 1),
+            (3, 8, 7, 7, 3, 1, 1), (2, 5, 13, 9, 5, 2, 2), (1, 2, 4, 30, 3, 1, 3)]
+
+
+@pytest.mark.parametrize("shape", GENERIC)
+@pytest.mark.parametrize("dt", ["f32", "f64", "f16", "bf16"])
+def test_generic_forward(shape, dt):
+    B, C, H, W, k, d, s = shape
+    dtype = DTYPES[dt]
+    x, cf, sf = make_inputs(B, C, H, W, k, s, dtype, seed=100 + k * 10 + d + s, with_go=False)
+    for m in ("mul", "add"):
+        out = _run(x, cf, sf, k, d, s, m, "o")
+        assert out.dtype == dtype and out.shape == (B, C, H // s, W // s)
+        check_close(out, oracle_forward(x, cf, sf, k, d, s, m), dtype, f"generic {shape} {dt} {m}")
+
+
+# ------------------------------------------------------------------ streaming kernel
+# B, C, H, W, k, d, s -- every (k, d, s, P) instantiation, plane runs that cross
+# sample boundaries inside a CTA, several samples inside one stage (small C),
+# fewer plane groups than SMs, and widths for each pixels-per-thread choice.
+STREAM = [
+    (4, 16, 56, 56, 3, 1, 1),    # P = 8
+    (3, 64, 28, 28, 3, 1, 1),    # P = 4, two planes per pass
+    (5, 32, 14, 14, 3, 1, 1),    # P = 2
+    (7, 64, 7, 7, 3, 1, 1),      # P = 1 (sub-word path for 2-byte types)
+    (40, 8, 7, 7, 3, 1, 1),      # C = planes per pass: a new sample every pass
+    (300, 2, 14, 14, 3, 1, 1),   # more samples than CTAs, two planes per sample
+    (3, 32, 56, 56, 3, 1, 2),    # stride 2, P = 4
+    (3, 32, 28, 28, 3, 1, 2),    # stride 2, P = 2
+    (3, 64, 14, 14, 3, 1, 2),    # stride 2, P = 1
+    (2, 16, 57, 56, 3, 1, 2),    # odd height at stride 2 (floor output size)
+    (3, 16, 56, 56, 3, 2, 1),    # dilation 2, P = 8
+    (3, 32, 28, 28, 3, 2, 1),
+    (3, 32, 14, 14, 3, 2, 1),
+    (3, 32, 28, 28, 5, 1, 1),    # k = 5
+    (3, 32, 14, 14, 5, 1, 1),
+    (3, 32, 28, 28, 5, 2, 1),
+    (2, 24, 20, 24, 3, 1, 1),    # non-square, H*W/8 = 60 tasks, 6 planes per pass
+    (1, 8, 40, 64, 3, 1, 1),     # wide plane, single sample
+    (2, 16, 16, 8, 3, 1, 1),
+]
+
+
+@pytest.mark.parametrize("shape", STREAM)
+@pytest.mark.parametrize("dt", ["f32", "f16", "bf16"])
+def test_stream_forward(shape, dt):
+    B, C, H, W, k, d, s = shape
+    dtype = DTYPES[dt]
+    x, cf, sf = make_inputs(B, C, H, W, k, s, dtype, seed=200 + H + k + d + s, with_go=False)
+    for m in ("mul", "add"):
+        out = _run(x, cf, sf, k, d, s, m, "f")
+        check_close(out, oracle_forward(x, cf, sf, k, d, s, m), dtype, f"stream {shape} {dt} {m}")
+    _no_fault()
+
+
+def test_stream_rejects_what_it_cannot_do():
+    from ddfnet_b200._lib import DDFError
+    x, cf, sf = make_inputs(1, 3, 9, 11, 7, 1, torch.float32, seed=1, with_go=False)
+    with pytest.raises(DDFError):
+        _run(x, cf, sf, 7, 1, 1, "mul", "f")
+
+
+def test_stream_writes_only_its_output():
+    """Canaries either side of the output buffer stay intact."""
+    from ddfnet_b200 import _lib
+    L = _lib.load()
+    dev = torch.device("cuda:0")
+    B, C, H, W = 3, 32, 28, 28
+    x, cf, sf = (t.to(dev) for t in make_inputs(B, C, H, W, 3, 1, torch.bfloat16, 5, with_go=False))
+    n = B * C * H * W
+    pad = 4096
+    buf = torch.full((n + 2 * pad,), 7.0, dtype=torch.bfloat16, device=dev)
+    out = buf[pad:pad + n]
+    for variant in (_lib.VARIANT_GENERIC, _lib.VARIANT_STREAM):
+        buf.fill_(7.0)
+        rc = L.ddf_b200_forward(x.data_ptr(), cf.data_ptr(), sf.data_ptr(), out.data_ptr(),
+                                B, C, H, W, 3, 1, 1, _lib.MUL, _lib.BF16, variant,
+                                torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert (buf[:pad] == 7.0).all() and (buf[pad + n:] == 7.0).all()
+        check_close(out.view(B, C, H, W), oracle_forward(x.cpu(), cf.cpu(), sf.cpu(), 3, 1, 1, "mul"),
+                    torch.bfloat16, "canary case")
+    _no_fault()
+
+
+# ------------------------------------------------------------------ the benchmark configurations
+def test_config1_fp32():
+    # single op, mul, float32: B=2, C=64, 56x56, k=3
+    x, cf, sf = make_inputs(2, 64, 56, 56, 3, 1, torch.float32, seed=1000, with_go=False)
+    want = oracle_forward(x, cf, sf, 3, 1, 1, "mul")
+    for ver in ("", "o", "f"):
+        check_close(_run(x, cf, sf, 3, 1, 1, "mul", ver), want, torch.float32, f"config 1 '{ver}'")
+    _no_fault()
+
+
+CONFIG2 = [(64, 56, 1), (128, 28, 1), (256, 14, 1), (512, 7, 1), (128, 56, 2), (256, 28, 2), (512, 14, 2)]
+
+
+@pytest.mark.parametrize("case", CONFIG2)
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+def test_config2_full_size(case, dt):
+    """ResNet-50 stage shapes at B = 128: the default kernel choice must be the
+    streaming kernel and must match the oracle; doubling the input doubles the
+    output exactly (a power-of-two scale commutes with every rounding)."""
+    C, H, s = case
+    B = 128
+    dtype = DTYPES[dt]
+    L = _lib().load()
+    assert L.ddf_b200_plan(B, C, H, H, 3, 1, s, 0, {"bf16": 2, "f16": 1}[dt], 0) == _lib().VARIANT_STREAM
+    x, cf, sf = make_inputs(B, C, H, H, 3, s, dtype, seed=2000 + C + s, with_go=False)
+    for m in ("mul", "add"):
+        out = _run(x, cf, sf, 3, 1, s, m)
+        check_close(out, oracle_forward(x, cf, sf, 3, 1, s, m), dtype, f"config 2 {case} {dt} {m}")
+        out2 = _run(x * 2, cf, sf, 3, 1, s, m)
+        assert torch.equal(out2, out * 2)
+    _no_fault()
+
+
+# ------------------------------------------------------------------ interface behaviour
+def test_interface_errors():
+    from ddfnet_b200 import ddf
+    dev = torch.device("cuda:0")
+    x, cf, sf = (t.to(dev) for t in make_inputs(2, 4, 8, 8, 3, 1, torch.float32, 3, with_go=False))
+    with pytest.raises(AssertionError):
+        ddf(x.cpu(), cf, sf, 3, 1, 1, "mul")
+    with pytest.raises(AssertionError):
+        ddf(x, cf[:, :3], sf, 3, 1, 1, "mul")
+    with pytest.raises(AssertionError):
+        ddf(x, cf, sf[:, :8], 3, 1, 1, "mul")
+    with pytest.raises(AssertionError):
+        ddf(x, cf, sf, 3, 1, 1, "max")
+    with pytest.raises(AssertionError):
+        ddf(x, cf, sf, 4, 1, 1, "mul")
+    with pytest.raises(RuntimeError):
+        ddf(x.transpose(2, 3), cf, sf, 3, 1, 1, "mul")
+    # mixed precision promotes, as the reference's float16 up-cast does
+    out = ddf(x.half(), cf, sf, 3, 1, 1, "mul")
+    assert out.dtype == torch.float32
+    # 7 positional arguments, as DDFPack calls it
+    assert ddf(x, cf, sf, 3, 1, 1, "add").shape == x.shape
+
+
+def test_runs_on_the_callers_stream():
+    from ddfnet_b200 import ddf
+    dev = torch.device("cuda:0")
+    x, cf, sf = (t.to(dev) for t in make_inputs(4, 64, 28, 28, 3, 1, torch.float16, 9, with_go=False))
+    want = oracle_forward(x.cpu(), cf.cpu(), sf.cpu(), 3, 1, 1, "mul")
+    st = torch.cuda.Stream()
+    st.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(st):
+        out = ddf(x, cf, sf, 3, 1, 1, "mul", "f")
+    st.synchronize()
+    check_close(out, want, torch.float16, "side stream")

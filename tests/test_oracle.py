@@ -1,0 +1,122 @@
+"""The CPU oracle is pinned here before anything is compared against it:
+against a restatement of the reference's own test oracle (py_forward,
+grad_check.py:11-30), against an independent unfold + autograd derivation in
+float64, against the committed fixtures in tests/golden/, and through the
+reference's gradcheck protocol (grad_check.py:139-299: float64, eps 1e-3,
+atol 1e-5) applied to an autograd Function that wraps the oracle."""
+import glob
+import os
+
+import pytest
+import torch
+
+from oracle import ddf_oracle as O
+
+CASES = [
+    # B, C, H, W, k, d, s, combine
+    (1, 10, 15, 15, 3, 2, 1, "mul"),   # grad_check.py:39-54
+    (1, 10, 15, 15, 3, 1, 1, "mul"),   # grad_check.py:58-73
+    (2, 5, 9, 11, 3, 1, 1, "add"),
+    (2, 3, 9, 11, 3, 1, 2, "mul"),
+    (1, 4, 13, 10, 5, 2, 2, "add"),
+    (2, 3, 8, 8, 5, 1, 1, "mul"),
+    (1, 3, 7, 7, 3, 2, 2, "add"),
+    (1, 2, 6, 6, 1, 1, 1, "mul"),
+    (1, 2, 9, 9, 7, 3, 1, "add"),
+    (1, 3, 5, 4, 3, 1, 3, "mul"),
+]
+
+
+def _rand(B, C, H, W, k, s, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, C, H, W, generator=g, dtype=torch.float64)
+    cf = torch.randn(B, C, k, k, generator=g, dtype=torch.float64)
+    sf = torch.randn(B, k * k, H // s, W // s, generator=g, dtype=torch.float64)
+    go = torch.randn(B, C, H // s, W // s, generator=g, dtype=torch.float64)
+    return x, cf, sf, go
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_oracle_matches_unfold_autograd(case):
+    B, C, H, W, k, d, s, m = case
+    x, cf, sf, go = _rand(B, C, H, W, k, s, 7)
+    xr, cfr, sfr = (t.clone().requires_grad_() for t in (x, cf, sf))
+    ref = O.composite_forward(xr, cfr, sfr, k, d, s, m)
+    ref.backward(go)
+    out = O.forward(x, cf, sf, k, d, s, m)
+    gx, gcf, gsf = O.backward(go, x, cf, sf, k, d, s, m)
+    for got, want in ((out, ref.detach()), (gx, xr.grad), (gcf, cfr.grad), (gsf, sfr.grad)):
+        assert (got - want).abs().max().item() <= 1e-12
+
+
+@pytest.mark.parametrize("case", [c for c in CASES if c[6] == 1 and c[0] * c[1] * c[2] * c[3] <= 3000])
+def test_oracle_matches_py_forward(case):
+    B, C, H, W, k, d, s, m = case
+    x, cf, sf, _ = _rand(B, C, H, W, k, s, 11)
+    want = O.py_forward_restatement(x, cf, sf, k, d, s, m)
+    got = O.forward(x, cf, sf, k, d, s, m)
+    # the reference accepts (py - ddf) <= 1e-10 (grad_check.py:44); two-sided here
+    assert (got - want).abs().max().item() <= 1e-10
+
+
+def test_oracle_f32_instance_close_to_f64():
+    x, cf, sf, go = _rand(2, 16, 20, 20, 3, 1, 3)
+    o64 = O.forward(x, cf, sf, 3, 1, 1, "mul")
+    o32 = O.forward(x.float(), cf.float(), sf.float(), 3, 1, 1, "mul")
+    assert (o32.double() - o64).abs().max().item() < 1e-4
+    g64 = O.backward(go, x, cf, sf, 3, 1, 1, "add")
+    g32 = O.backward(go.float(), x.float(), cf.float(), sf.float(), 3, 1, 1, "add")
+    for a, b in zip(g32, g64):
+        assert (a.double() - b).abs().max().item() < 1e-3
+
+
+class _OracleOp(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cf, sf, k, d, s, m):
+        ctx.cfg = (k, d, s, m)
+        ctx.save_for_backward(x, cf, sf)
+        return O.forward(x, cf, sf, k, d, s, m)
+
+    @staticmethod
+    def backward(ctx, go):
+        x, cf, sf = ctx.saved_tensors
+        k, d, s, m = ctx.cfg
+        gx, gcf, gsf = O.backward(go.contiguous(), x, cf, sf, k, d, s, m)
+        return gx, gcf, gsf, None, None, None, None
+
+
+# The reference's six gradcheck shape families, shrunk along the long axis so
+# that the numerical Jacobians stay small (grad_check.py:139-299).
+GRADCHECK = [
+    (1, 7, 6, 6, 3), (5, 1, 6, 6, 3), (1, 1, 12, 12, 3),
+    (1, 7, 6, 6, 5), (4, 1, 6, 6, 5), (1, 1, 10, 10, 5),
+]
+
+
+@pytest.mark.parametrize("shape", GRADCHECK)
+@pytest.mark.parametrize("d", [1, 2])
+@pytest.mark.parametrize("s", [1, 2])
+@pytest.mark.parametrize("m", ["mul", "add"])
+def test_oracle_gradcheck(shape, d, s, m):
+    B, C, H, W, k = shape
+    x, cf, sf, _ = _rand(B, C, H, W, k, s, 5)
+    x.requires_grad_(); cf.requires_grad_(); sf.requires_grad_()
+    assert torch.autograd.gradcheck(
+        lambda a, b, c: _OracleOp.apply(a, b, c, k, d, s, m), (x, cf, sf), eps=1e-3, atol=1e-5)
+
+
+def test_oracle_matches_golden_fixtures():
+    files = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.pt")))
+    assert files, "no golden fixtures committed"
+    for f in files:
+        fx = torch.load(f)
+        k, d, s, m = fx["k"], fx["d"], fx["s"], fx["combine"]
+        x, cf, sf, go = (fx[n].double() for n in ("x", "cf", "sf", "go"))
+        tol = fx.get("tol", 1e-9)
+        out = O.forward(x, cf, sf, k, d, s, m)
+        assert (out - fx["out"].double()).abs().max().item() <= tol, f
+        gx, gcf, gsf = O.backward(go, x, cf, sf, k, d, s, m)
+        for name, got in (("gx", gx), ("gcf", gcf), ("gsf", gsf)):
+            if name in fx:
+                scale = max(1.0, fx[name].double().abs().max().item())
+                assert (got - fx[name].double()).abs().max().item() <= tol * scale, (f, name)
