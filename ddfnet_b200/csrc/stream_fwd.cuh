@@ -42,8 +42,9 @@ namespace ddf {
 
 constexpr int kMaxSlots = 16;          // ring depth upper bound
 constexpr int kMaxComputeThreads = 416;  // 13 warps; + 1 service warp = 448 threads
+// 14 warps = 4 per SM sub-partition at most; each sub-partition has 16K registers,
+// so a thread may use up to 128 (the launch bound below makes ptxas keep to that).
 constexpr int kStreamThreads = kMaxComputeThreads + 32;
-constexpr int kStreamMaxRegs = 144;          // 448 threads x 144 registers fit one SM's 64K
 constexpr uint32_t kSmemBudget = 225 * 1024;
 
 struct StreamPlan {
@@ -181,7 +182,7 @@ __device__ __forceinline__ bool warp_test(uint32_t bar, uint32_t parity, int lan
 // BWDX = true : out = grad-x computed from `in` (= go); stride must be 1.
 // PACK        : accumulate with packed f32x2 FMAs (two pixels per instruction).
 template <typename T, int K, int D, int S, int P, int MODE, bool BWDX, bool PACK>
-__global__ void __maxnreg__(kStreamMaxRegs)
+__global__ void __launch_bounds__(kStreamThreads, 1)
 stream_kernel(const __grid_constant__ StreamPlan pl) {
     using G = Geo<T, K, D, S, P>;
     constexpr int KK = G::KK;

@@ -90,6 +90,9 @@ class DDFFunction(Function):
         ctx.stride = stride
         ctx.op_type = kernel_combine
         ctx.variant = _VARIANT[version]
+        # as in the reference, 'f' selects a forward kernel only (its backward always
+        # runs the non-"faster" module, ddf/ddf.py:71,103,114)
+        ctx.bwd_variant = _lib.VARIANT_GENERIC if version == 'o' else _lib.VARIANT_AUTO
 
         output = torch.empty((b, c, h // stride, w // stride), dtype=dt, device=features.device)
         lib = _lib.load()
@@ -120,14 +123,14 @@ class DDFFunction(Function):
         lib = _lib.load()
         comb, dtc = _COMBINE[ctx.op_type], _DTYPES[dt]
         with torch.cuda.device(dev):
-            ws_bytes = int(lib.ddf_b200_backward_workspace(b, c, h, w, k, d, s, comb, dtc, ctx.variant))
+            ws_bytes = int(lib.ddf_b200_backward_workspace(b, c, h, w, k, d, s, comb, dtc, ctx.bwd_variant))
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
             stream = torch.cuda.current_stream().cuda_stream
             ptr = lambda t: t.data_ptr() if t is not None else None
             _lib.check(lib.ddf_b200_backward(
                 grad_output.data_ptr(), features.data_ptr(), channel_filter.data_ptr(),
                 spatial_filter.data_ptr(), ptr(gx), ptr(gcf), ptr(gsf), ptr(ws), ws_bytes,
-                b, c, h, w, k, d, s, comb, dtc, ctx.variant, stream))
+                b, c, h, w, k, d, s, comb, dtc, ctx.bwd_variant, stream))
         dx, dcf, dsf = ctx.in_dtypes
         if gx is not None and gx.dtype != dx:
             gx = gx.to(dx)

@@ -8,9 +8,11 @@ Tolerances (stated by the project's target):
   float16  : <= 2e-3 relative
   bfloat16 : <= 2e-3 relative *on top of the final rounding to bfloat16*: a
              correctly rounded bfloat16 value is itself up to 2**-8 = 3.9e-3
-             away from the exact one, so a bare 2e-3 element-wise bound cannot be
-             met by any implementation; the aggregate (relative L2) error is
-             held to 2e-3 as stated.
+             away from the exact one (1.6e-3 .. 2.3e-3 in the RMS), so a bare
+             2e-3 bound against the exact value cannot be met by any
+             implementation.
+  Both 2-byte types are also held, in the aggregate, to a relative L2 distance
+  of 2e-3 from the oracle result rounded to the storage type.
 """
 from __future__ import annotations
 
@@ -67,5 +69,6 @@ def check_close(actual, expected64, dtype, what=""):
             f"{what}: {int(bad.sum())} of {b.numel()} elements out of tolerance; first at {i}: "
             f"got {a[tuple(i)].item()!r} want {b[tuple(i)].item()!r}; worst err/bound {worst:.3g}")
     if dtype in (torch.float16, torch.bfloat16):
-        rel_l2 = (err.pow(2).sum() / b.pow(2).sum().clamp_min(1e-30)).sqrt().item()
-        assert rel_l2 <= 2e-3, f"{what}: relative L2 error {rel_l2:.3e} > 2e-3"
+        b_rounded = b.to(dtype).to(torch.float64)
+        rel_l2 = ((a - b_rounded).pow(2).sum() / b.pow(2).sum().clamp_min(1e-30)).sqrt().item()
+        assert rel_l2 <= 2e-3, f"{what}: relative L2 distance {rel_l2:.3e} > 2e-3"
