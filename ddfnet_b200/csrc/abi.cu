@@ -344,7 +344,7 @@ int ddf_b200_backward(const void* go, const void* x, const void* cf, const void*
             if (need > 0 && (!workspace || workspace_bytes < need)) return DDF_B200_E_WORKSPACE;
             int launches = 0;
             rc = bwd_stream_filters(p, go, x, cf, sf, gcf, gsf, workspace, di->sm_count, di->fault,
-                                    st, &launches);
+                                    di->index, st, &launches);
             if (rc == 0) {
                 done = true;
                 g_launches.fetch_add((unsigned long long)launches, std::memory_order_relaxed);

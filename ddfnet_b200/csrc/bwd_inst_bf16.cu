@@ -1,0 +1,3 @@
+// Filter-gradient streaming kernel instantiations for __nv_bfloat16 elements.
+#define DDF_INST_T __nv_bfloat16
+#include "bwd_inst.inc"

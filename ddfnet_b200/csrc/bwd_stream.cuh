@@ -19,6 +19,6 @@ size_t bwd_stream_workspace(const Problem& p, int sm_count);
 // kNotHandled, or a CUDA error; *launches receives the number of launches.
 int bwd_stream_filters(const Problem& p, const void* go, const void* x, const void* cf,
                        const void* sf, void* gcf, void* gsf, void* workspace, int sm_count,
-                       int* fault, cudaStream_t st, int* launches);
+                       int* fault, int device, cudaStream_t st, int* launches);
 
 }  // namespace ddf

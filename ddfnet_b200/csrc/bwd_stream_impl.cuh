@@ -1,0 +1,614 @@
+// Plane-streaming kernel for the two filter gradients of the DDF op:
+//
+//   gcf[b,c,t]   = sum_{y,x} go[b,c,y,x] * x[b,c,y*s+oi,x*s+oj] * (sf[b,t,y,x] | 1)
+//   gsf[b,t,y,x] = sum_c     go[b,c,y,x] * x[b,c,y*s+oi,x*s+oj] * (cf[b,c,t]   | 1)
+//
+// (the factor in parentheses is present for 'mul' and absent for 'add').  Both
+// share the product go * x, so one pass over go and x produces both.
+//
+// The structure is that of the forward streaming kernel (stream_fwd.cuh): a
+// persistent grid, each CTA owning a contiguous run of (b, c) planes; a service
+// warp feeds go planes, x planes and channel filters through a ring of
+// shared-memory stages with bulk async copies; every compute thread owns P output
+// pixels for the whole kernel.
+//
+//   gsf  is a sum over channels at fixed pixel: each thread accumulates its
+//        k*k*P values in registers while its CTA walks the channels of a sample
+//        and writes them, as float partial sums, to a scratch slot when the run
+//        leaves the sample (or ends).  A sample's channels may be split over a
+//        few CTAs; gsf_reduce_kernel adds the slots in a fixed order (no atomics,
+//        so the result is deterministic) and rounds to the element type.
+//   gcf  is a sum over pixels at fixed channel: each thread forms k*k partial
+//        sums per plane, a warp folds them with a multi-value butterfly (12
+//        shuffles for 9 values instead of 45) and leaves one value per warp and
+//        tap in the stage's shared-memory slot; when a stage is released the
+//        service warp adds the per-warp values and stores gcf.
+//
+// Threads of one plane are padded to whole warps so that a warp never mixes
+// two planes.
+#pragma once
+
+#include "stream_fwd.cuh"
+
+namespace ddf {
+
+constexpr int kBwdComputeThreads = 448;  // 14 warps; + 1 service warp = 480 threads
+constexpr int kBwdThreads = kBwdComputeThreads + 32;
+
+struct BwdPlan {
+    const void* go;
+    const void* x;
+    const void* cf;
+    const void* sf;
+    void* gcf;       // may be null
+    float* scratch;  // gsf partial sums; null when gsf is not wanted
+    int C, H, W, OH, OW;
+    int tasks_per_plane;   // OH*OW / P
+    int tasks_padded;      // rounded up to a multiple of 32
+    int groups_per_row;
+    int planes_per_pass;
+    int passes_per_stage;
+    int n_slots;
+    int n_compute_warps;
+    int warps_per_plane;
+    long long total_passes;
+    uint32_t xplane_bytes, gplane_bytes, sf_bytes;
+    uint32_t off_zero, off_cfc, cfc_stride, off_sf, off_stage0, stage_stride;
+    uint32_t off_x, off_rawcf, off_gpart;  // inside a stage
+    int* fault;
+};
+
+// Folds GROUP per-lane values across the warp.  On return lanes whose `slot`
+// (precomputed by butterfly_slot) is >= 0 hold in v[0] the warp total of value
+// number `slot`.
+template <int GROUP>
+__device__ __forceinline__ void butterfly_reduce(float (&v)[GROUP], int lane) {
+    int n = GROUP;
+#pragma unroll
+    for (int lvl = 0; lvl < 5; ++lvl) {
+        const int o = 16 >> lvl;
+        const int lo = (n + 1) / 2;
+        const bool upper = (lane & o) != 0;
+#pragma unroll
+        for (int i = 0; i < lo; ++i) {
+            const float keep_lo = v[i];
+            const float keep_hi = (lo + i < n) ? v[lo + i] : 0.f;
+            const float recv = __shfl_xor_sync(0xffffffffu, upper ? keep_lo : keep_hi, o);
+            v[i] = (upper ? keep_hi : keep_lo) + recv;
+        }
+        n = lo;
+    }
+}
+
+// Which of the GROUP values ends up in this lane (-1: none).
+template <int GROUP>
+__device__ __forceinline__ int butterfly_slot(int lane) {
+    int a = 0, b = GROUP;
+#pragma unroll
+    for (int lvl = 0; lvl < 5; ++lvl) {
+        const int lo = (b - a + 1) / 2;
+        if (lane & (16 >> lvl)) a += lo; else b = a + lo;
+    }
+    return a < b ? a : -1;
+}
+
+template <typename T, int K, int D, int S, int P, int MODE>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
+    using G = Geo<T, K, D, S, P>;
+    constexpr int KK = G::KK;
+    constexpr int ES = G::ES;
+    constexpr bool MUL = MODE == DDF_B200_MUL;
+    // values folded per butterfly: all taps at once for k = 3, one tap row for k = 5
+    constexpr int GROUP = (K == 3) ? KK : K;
+    constexpr int ROWS_PER_GROUP = GROUP / K;
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const uint32_t sbase = smem_u32(smem_raw);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int NST = pl.n_slots;
+    const int NCW = pl.n_compute_warps;
+    const int NP = pl.planes_per_pass;
+    const int PPS = pl.passes_per_stage;
+    const int WPP = pl.warps_per_plane;
+
+    const uint32_t bar_sf_full = sbase + 8u * (3 * kMaxSlots);
+    const uint32_t bar_sf_empty = bar_sf_full + 8u;
+#define BAR_FULL(s) (sbase + 8u * (uint32_t)(s))
+#define BAR_EMPTY(s) (sbase + 8u * (uint32_t)(kMaxSlots + (s)))
+#define BAR_READY(s) (sbase + 8u * (uint32_t)(2 * kMaxSlots + (s)))
+#define STAGE_BASE(s) (sbase + pl.off_stage0 + (uint32_t)(s) * pl.stage_stride)
+
+    if (tid == 0) {
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(BAR_FULL(s), 1);
+            mbar_init(BAR_EMPTY(s), (uint32_t)NCW);
+            mbar_init(BAR_READY(s), 1);
+        }
+        mbar_init(bar_sf_full, 1);
+        mbar_init(bar_sf_empty, (uint32_t)NCW);
+        mbar_fence_init();
+    }
+    if (tid < 64) sts32(sbase + pl.off_zero + 4u * tid, 0u);
+    __syncthreads();
+
+    const long long pass_lo = (pl.total_passes * (long long)blockIdx.x) / gridDim.x;
+    const long long pass_hi = (pl.total_passes * (long long)(blockIdx.x + 1)) / gridDim.x;
+    const int my_passes = (int)(pass_hi - pass_lo);
+    if (my_passes == 0) return;
+    const int my_stages = (my_passes + PPS - 1) / PPS;
+    const long long plane_lo = pass_lo * NP, plane_hi = pass_hi * NP;
+    const int stage_planes = PPS * NP;
+
+    if (warp == NCW) {
+        // ------------------------------------------------------------- service warp
+        int issue_i = 0, conv_j = 0, red_r = 0, seg_k = 0;
+        long long seg_b = plane_lo / pl.C;
+        long long seg_plane = plane_lo;
+        long long idle_since = -1;
+        bool gave_up = false;
+        while (red_r < my_stages || (MUL && seg_plane < plane_hi)) {
+            bool progress = false;
+            // (1) spatial filter of the next sample ('mul' only), see stream_fwd.cuh
+            if constexpr (MUL) {
+                const int ahead = issue_i + 1 < my_stages ? issue_i + 1 : my_stages;
+                long long horizon = plane_lo + (long long)ahead * stage_planes;
+                if (horizon > plane_hi) horizon = plane_hi;
+                if (seg_plane < horizon &&
+                    (seg_k == 0 || warp_test(bar_sf_empty, (uint32_t)((seg_k - 1) & 1), lane))) {
+                    if (lane == 0) {
+                        const unsigned long long g0 = (unsigned long long)seg_b * pl.sf_bytes;
+                        const unsigned long long a0 = g0 & ~15ull;
+                        const unsigned long long a1 = (g0 + pl.sf_bytes + 15ull) & ~15ull;
+                        mbar_arrive_expect_tx(bar_sf_full, (uint32_t)(a1 - a0));
+                        bulk_g2s(sbase + pl.off_sf, (const char*)pl.sf + a0, (uint32_t)(a1 - a0),
+                                 bar_sf_full);
+                    }
+                    ++seg_k;
+                    ++seg_b;
+                    seg_plane = seg_b * pl.C;
+                    progress = true;
+                }
+            }
+            // (2) next stage: its slot is reusable once the stage that used it has been
+            // released by the compute warps AND its channel-filter-gradient partials
+            // have been folded (red_r counts folded stages).
+            if (issue_i < my_stages && (issue_i < NST || red_r > issue_i - NST)) {
+                const int slot = issue_i % NST;
+                const long long st_first = plane_lo + (long long)issue_i * stage_planes;
+                long long st_end = st_first + stage_planes;
+                if (st_end > plane_hi) st_end = plane_hi;
+                if (lane == 0) {
+                    const unsigned long long n0 = (unsigned long long)st_first, n1 = (unsigned long long)st_end;
+                    const unsigned long long x0 = (n0 * pl.xplane_bytes) & ~15ull;
+                    const unsigned long long x1 = (n1 * pl.xplane_bytes + 15ull) & ~15ull;
+                    const unsigned long long g0 = (n0 * pl.gplane_bytes) & ~15ull;
+                    const unsigned long long g1 = (n1 * pl.gplane_bytes + 15ull) & ~15ull;
+                    const unsigned long long c0 = (n0 * (KK * ES)) & ~15ull;
+                    const unsigned long long c1 = (n1 * (KK * ES) + 15ull) & ~15ull;
+                    uint32_t bytes = (uint32_t)((x1 - x0) + (g1 - g0));
+                    if constexpr (MUL) bytes += (uint32_t)(c1 - c0);
+                    mbar_arrive_expect_tx(BAR_FULL(slot), bytes);
+                    bulk_g2s(STAGE_BASE(slot) + 32u, (const char*)pl.go + g0, (uint32_t)(g1 - g0),
+                             BAR_FULL(slot));
+                    bulk_g2s(STAGE_BASE(slot) + pl.off_x, (const char*)pl.x + x0, (uint32_t)(x1 - x0),
+                             BAR_FULL(slot));
+                    if constexpr (MUL)
+                        bulk_g2s(STAGE_BASE(slot) + pl.off_rawcf, (const char*)pl.cf + c0,
+                                 (uint32_t)(c1 - c0), BAR_FULL(slot));
+                }
+                ++issue_i;
+                progress = true;
+            }
+            if (conv_j < issue_i) {
+                const int slot = conv_j % NST;
+                if (warp_test(BAR_FULL(slot), (uint32_t)((conv_j / NST) & 1), lane)) {
+                    if constexpr (MUL) {
+                        const long long st_first = plane_lo + (long long)conv_j * stage_planes;
+                        long long st_end = st_first + stage_planes;
+                        if (st_end > plane_hi) st_end = plane_hi;
+                        const int n = (int)(st_end - st_first) * KK;
+                        const uint32_t coff = (uint32_t)(((unsigned long long)st_first * (KK * ES)) & 15ull);
+                        const uint32_t src = STAGE_BASE(slot) + pl.off_rawcf + coff;
+                        const uint32_t dst = sbase + pl.off_cfc + (uint32_t)slot * pl.cfc_stride;
+                        for (int e = lane; e < n; e += 32) {
+                            float v;
+                            if constexpr (ES == 4) v = ldsf(src + 4u * e);
+                            else v = Word<T>::get(lds16(src + 2u * e), 0);
+                            sts32(dst + 4u * e, __float_as_uint(v));
+                        }
+                        __syncwarp();
+                    }
+                    if (lane == 0) mbar_arrive(BAR_READY(slot));
+                    ++conv_j;
+                    progress = true;
+                }
+            }
+            if (red_r < conv_j) {
+                const int slot = red_r % NST;
+                if (warp_test(BAR_EMPTY(slot), (uint32_t)((red_r / NST) & 1), lane)) {
+                    // Fold the per-warp partial sums of this stage and store gcf.
+                    const long long st_first = plane_lo + (long long)red_r * stage_planes;
+                    long long st_end = st_first + stage_planes;
+                    if (st_end > plane_hi) st_end = plane_hi;
+                    const int n = (int)(st_end - st_first) * KK;
+                    if (pl.gcf != nullptr) {
+                        T* dst = reinterpret_cast<T*>(pl.gcf) + st_first * KK;
+                        const uint32_t src = STAGE_BASE(slot) + pl.off_gpart;
+                        for (int e = lane; e < n; e += 32) {
+                            const int plane = e / KK, t = e - plane * KK;
+                            float tot = 0.f;
+                            for (int w = 0; w < WPP; ++w)
+                                tot += ldsf(src + 4u * (uint32_t)((plane * WPP + w) * KK + t));
+                            Elem<T>::store(dst + e, tot);
+                        }
+                    }
+                    __syncwarp();
+                    ++red_r;
+                    progress = true;
+                }
+            }
+            if (progress) {
+                idle_since = -1;
+            } else if (idle_since < 0) {
+                idle_since = clock64();
+            } else if (clock64() - idle_since > kWaitCycles) {
+                gave_up = true;
+                break;
+            }
+        }
+        if (gave_up) {
+            if (lane == 0) atomicCAS(pl.fault, 0, (int)kFaultService);
+            bool drained = true;
+            for (int j = conv_j; j < issue_i; ++j)
+                drained &= mbar_wait(BAR_FULL(j % NST), (uint32_t)((j / NST) & 1));
+            if (MUL && seg_k > 0) drained &= mbar_wait(bar_sf_full, (uint32_t)((seg_k - 1) & 1));
+            if (!drained && lane == 0) atomicExch(pl.fault, (int)kFaultDrain);
+        }
+        return;
+    }
+    if (warp > NCW) return;
+
+    // ----------------------------------------------------------------- compute warps
+    const int TP = pl.tasks_per_plane;
+    const int TPW = pl.tasks_padded;
+    const int pip = tid / TPW;  // plane within the pass; a warp never straddles two
+    int task = tid - pip * TPW;
+    const bool active = task < TP;
+    if (!active) task = 0;
+    const int wip = (tid - pip * TPW) >> 5;  // warp within the plane
+    const int oy = task / pl.groups_per_row;
+    const int ox0 = (task - oy * pl.groups_per_row) * P;
+
+    bool rowok[K];
+    uint32_t rowoff[K];
+#pragma unroll
+    for (int i = 0; i < K; ++i) {
+        const int iy = oy * S + (i - G::R) * D;
+        rowok[i] = iy >= 0 && iy < pl.H;
+        rowoff[i] = (uint32_t)((iy * pl.W + ox0 * S) * ES);
+    }
+    uint32_t lmask[G::NLM], rmask[G::NRM];
+    halo_masks<G>(ox0, S, pl.W, lmask, rmask);
+    const uint32_t zero_row = sbase + pl.off_zero + 64u;
+    const uint32_t go_off = (uint32_t)((oy * pl.OW + ox0) * ES);
+    const int my_slot = butterfly_slot<GROUP>(lane);
+
+    float sfr[MUL ? KK : 1][P];
+    float gsf[KK][P];
+#pragma unroll
+    for (int t = 0; t < KK; ++t)
+#pragma unroll
+        for (int pp = 0; pp < P; ++pp) gsf[t][pp] = 0.f;
+
+    long long b = plane_lo / pl.C;
+    int c_in_b = (int)(plane_lo - b * pl.C);
+    bool need_sf = true;
+    int seg = 0;
+    const long long opl = (long long)pl.OH * pl.OW;
+
+    auto flush = [&](long long sample) {
+        if (pl.scratch != nullptr && active) {
+            float* dst = pl.scratch + (((sample + blockIdx.x) * NP + pip) * KK) * opl +
+                         (long long)oy * pl.OW + ox0;
+#pragma unroll
+            for (int t = 0; t < KK; ++t) {
+                if constexpr (P == 1) {
+                    dst[t * opl] = gsf[t][0];
+                } else if constexpr (P == 2) {
+                    *reinterpret_cast<float2*>(dst + t * opl) = make_float2(gsf[t][0], gsf[t][1]);
+                } else {
+#pragma unroll
+                    for (int v = 0; v < P / 4; ++v)
+                        reinterpret_cast<float4*>(dst + t * opl)[v] =
+                            make_float4(gsf[t][4 * v], gsf[t][4 * v + 1], gsf[t][4 * v + 2], gsf[t][4 * v + 3]);
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < KK; ++t)
+#pragma unroll
+            for (int pp = 0; pp < P; ++pp) gsf[t][pp] = 0.f;
+    };
+
+    for (int st = 0; st < my_stages; ++st) {
+        const int slot = st % NST;
+        const uint32_t ph = (uint32_t)((st / NST) & 1);
+        if (!mbar_wait(BAR_FULL(slot), ph) || !mbar_wait(BAR_READY(slot), ph)) {
+            atomicCAS(pl.fault, 0, (int)kFaultConsumerFull);
+            return;
+        }
+        const int first_pass = st * PPS;
+        const int npass = (my_passes - first_pass) < PPS ? (my_passes - first_pass) : PPS;
+        const unsigned long long sfp = (unsigned long long)plane_lo + (unsigned long long)first_pass * NP;
+        const uint32_t xoff = (uint32_t)((sfp * pl.xplane_bytes) & 15ull);
+        const uint32_t goff = (uint32_t)((sfp * pl.gplane_bytes) & 15ull);
+        uint32_t xplane_s = STAGE_BASE(slot) + pl.off_x + xoff + (uint32_t)pip * pl.xplane_bytes;
+        uint32_t gplane_s = STAGE_BASE(slot) + 32u + goff + (uint32_t)pip * pl.gplane_bytes + go_off;
+        uint32_t cfc_s = sbase + pl.off_cfc + (uint32_t)slot * pl.cfc_stride + (uint32_t)pip * (KK * 4);
+        uint32_t gpart_s = STAGE_BASE(slot) + pl.off_gpart + 4u * (uint32_t)((pip * WPP + wip) * KK);
+
+        for (int q = 0; q < npass; ++q) {
+            if constexpr (MUL) {
+                if (need_sf) {
+                    if (!mbar_wait(bar_sf_full, (uint32_t)(seg & 1))) {
+                        atomicCAS(pl.fault, 0, (int)kFaultConsumerSf);
+                        return;
+                    }
+                    const uint32_t sfs =
+                        sbase + pl.off_sf + (uint32_t)(((unsigned long long)b * pl.sf_bytes) & 15ull);
+#pragma unroll
+                    for (int t = 0; t < KK; ++t) {
+                        const uint32_t a = sfs + (uint32_t)(((t * pl.OH + oy) * pl.OW + ox0) * ES);
+                        if constexpr (G::OUTB < 4) {
+                            sfr[t][0] = Word<T>::get(lds16(a), 0);
+                        } else {
+                            uint32_t w[G::OUTB / 4];
+                            lds_vec<G::OUTB>(a, w);
+#pragma unroll
+                            for (int pp = 0; pp < P; ++pp)
+                                sfr[t][pp] = Word<T>::get(w[pp / G::EPW], pp % G::EPW);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_sf_empty);
+                    ++seg;
+                    need_sf = false;
+                }
+            }
+
+            // upstream gradient at this thread's pixels
+            float g[P];
+            if constexpr (G::OUTB < 4) {
+                g[0] = Word<T>::get(lds16(gplane_s), 0);
+            } else {
+                uint32_t w[G::OUTB / 4];
+                lds_vec<G::OUTB>(gplane_s, w);
+#pragma unroll
+                for (int pp = 0; pp < P; ++pp) g[pp] = Word<T>::get(w[pp / G::EPW], pp % G::EPW);
+            }
+
+#pragma unroll
+            for (int i0 = 0; i0 < K; i0 += ROWS_PER_GROUP) {
+                float part[GROUP];
+#pragma unroll
+                for (int u = 0; u < GROUP; ++u) part[u] = 0.f;
+#pragma unroll
+                for (int ii = 0; ii < ROWS_PER_GROUP; ++ii) {
+                    const int i = i0 + ii;
+                    const uint32_t rp = rowok[i] ? (xplane_s + rowoff[i]) : zero_row;
+                    float xr[G::NCOL];
+                    load_row<T, G>(rp, lmask, rmask, xr);
+#pragma unroll
+                    for (int j = 0; j < K; ++j) {
+                        const int t = i * K + j;
+                        float c = 1.f;
+                        if constexpr (MUL) c = ldsf(cfc_s + 4u * t);
+#pragma unroll
+                        for (int pp = 0; pp < P; ++pp) {
+                            const float prod = g[pp] * xr[pp * S + j * D];
+                            if constexpr (MUL) {
+                                gsf[t][pp] = fmaf(prod, c, gsf[t][pp]);
+                                part[ii * K + j] = fmaf(prod, sfr[t][pp], part[ii * K + j]);
+                            } else {
+                                gsf[t][pp] += prod;
+                                part[ii * K + j] += prod;
+                            }
+                        }
+                    }
+                }
+                if (!active) {
+#pragma unroll
+                    for (int u = 0; u < GROUP; ++u) part[u] = 0.f;
+                }
+                butterfly_reduce<GROUP>(part, lane);
+                if (my_slot >= 0) sts32(gpart_s + 4u * (uint32_t)(i0 * K + my_slot), __float_as_uint(part[0]));
+            }
+
+            xplane_s += (uint32_t)NP * pl.xplane_bytes;
+            gplane_s += (uint32_t)NP * pl.gplane_bytes;
+            cfc_s += (uint32_t)NP * (KK * 4);
+            gpart_s += 4u * (uint32_t)(NP * WPP * KK);
+            c_in_b += NP;
+            if (c_in_b >= pl.C) {
+                flush(b);
+                c_in_b = 0;
+                ++b;
+                need_sf = true;
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(BAR_EMPTY(slot));
+    }
+    if (c_in_b != 0) flush(b);
+#undef BAR_FULL
+#undef BAR_EMPTY
+#undef BAR_READY
+#undef STAGE_BASE
+}
+
+// gsf[b, e] = sum over the CTAs whose plane run touched sample b, and over the
+// planes-per-pass lanes of each, of their float partials; fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gsf_reduce_kernel(const float* __restrict__ scratch, T* __restrict__ gsf, int B, int C, int NP,
+                  long long n_per_sample, long long total_passes, int grid_main) {
+    for (long long b = blockIdx.y; b < B; b += gridDim.y) {
+        // passes of sample b, and the CTAs of the main kernel that owned them
+        const long long q0 = b * C / NP, q1 = (b + 1) * C / NP - 1;
+        const long long c0 = ((q0 + 1) * grid_main - 1) / total_passes;
+        const long long c1 = ((q1 + 1) * grid_main - 1) / total_passes;
+        for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < n_per_sample;
+             e += (long long)gridDim.x * blockDim.x) {
+            float tot = 0.f;
+            for (long long c = c0; c <= c1; ++c)
+                for (int u = 0; u < NP; ++u) tot += scratch[((b + c) * NP + u) * n_per_sample + e];
+            Elem<T>::store(gsf + b * n_per_sample + e, tot);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------ host side
+struct BwdArgs {
+    const void* go;
+    const void* x;
+    const void* cf;
+    const void* sf;
+    void* gcf;
+    void* gsf;
+    void* workspace;
+    Problem p;
+    int sm_count;
+    int* fault;
+    int P;
+    int device;
+};
+
+struct BwdGeometry {
+    int P, TP, TPW, NP, grid;
+    long long total_passes;
+};
+
+// Thread layout shared by the launcher, the workspace query and the reducer.
+inline bool bwd_geometry(const Problem& p, int P, int sm_count, BwdGeometry& g) {
+    if (p.OW % P != 0 || p.W != p.OW * p.s) return false;
+    const int TP = p.OH * p.OW / P;
+    const int TPW = (TP + 31) / 32 * 32;
+    if (TP < 1 || TPW > kBwdComputeThreads) return false;
+    int NP = kBwdComputeThreads / TPW;
+    while (NP > 1 && p.C % NP != 0) --NP;
+    g.P = P; g.TP = TP; g.TPW = TPW; g.NP = NP;
+    g.total_passes = (long long)p.B * p.C / NP;
+    g.grid = (int)(g.total_passes < sm_count ? g.total_passes : sm_count);
+    return true;
+}
+
+inline size_t bwd_workspace_bytes(const Problem& p, const BwdGeometry& g) {
+    return (size_t)(p.B + g.grid) * g.NP * p.k * p.k * p.OH * p.OW * sizeof(float);
+}
+
+template <typename T, int K, int D, int S, int P>
+bool make_bwd_plan(const BwdArgs& a, BwdPlan& pl, uint32_t& smem_bytes, BwdGeometry& g) {
+    using G = Geo<T, K, D, S, P>;
+    const Problem& p = a.p;
+    if (!bwd_geometry(p, P, a.sm_count, g)) return false;
+    const long long planes = (long long)p.B * p.C;
+    const uint32_t xpb = (uint32_t)(p.H * p.W * G::ES);
+    const uint32_t gpb = (uint32_t)(p.OH * p.OW * G::ES);
+    const uint32_t sfb = (uint32_t)(G::KK * p.OH * p.OW * G::ES);
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    if (!al16(a.go) || !al16(a.x) || !al16(a.cf) || !al16(a.sf)) return false;
+    if (a.workspace && !al16(a.workspace)) return false;
+    if ((planes * xpb) % 16 != 0 || (planes * gpb) % 16 != 0) return false;
+    if ((planes * G::KK * G::ES) % 16 != 0) return false;
+    if (((long long)p.B * sfb) % 16 != 0) return false;
+
+    int PPS = (int)(16384u / ((uint32_t)g.NP * (xpb + gpb)));
+    if (PPS < 1) PPS = 1;
+    const long long share = (g.total_passes + a.sm_count - 1) / a.sm_count;
+    if (PPS > share) PPS = (int)share;
+    if (PPS < 1) PPS = 1;
+    const int SPL = PPS * g.NP;
+    const int WPP = g.TPW / 32;
+
+    pl.off_zero = 512;
+    pl.off_cfc = pl.off_zero + 256;
+    pl.cfc_stride = round_up((uint32_t)SPL * G::KK * 4u, 16);
+    const uint32_t go_region = 32u + (uint32_t)SPL * gpb + 16u + 32u;
+    pl.off_x = round_up(go_region, 16) + 32u;
+    const uint32_t x_end = pl.off_x + (uint32_t)SPL * xpb + 16u + 32u;
+    pl.off_rawcf = round_up(x_end, 16);
+    pl.off_gpart = round_up(pl.off_rawcf + (uint32_t)SPL * G::KK * G::ES + 32u, 16);
+    pl.stage_stride = round_up(pl.off_gpart + (uint32_t)SPL * WPP * G::KK * 4u, 128);
+    const uint32_t sf_region = round_up(sfb + 32u, 128);
+    int slots = kMaxSlots;
+    for (;; --slots) {
+        if (slots < 2) return false;
+        const uint32_t off_sf = round_up(pl.off_cfc + (uint32_t)slots * pl.cfc_stride, 128);
+        const uint32_t total = off_sf + sf_region + (uint32_t)slots * pl.stage_stride;
+        if (total <= kSmemBudget) {
+            pl.off_sf = off_sf;
+            pl.off_stage0 = off_sf + sf_region;
+            smem_bytes = total;
+            break;
+        }
+    }
+    pl.n_slots = slots;
+    pl.go = a.go; pl.x = a.x; pl.cf = a.cf; pl.sf = a.sf;
+    pl.gcf = a.gcf;
+    pl.scratch = a.gsf ? reinterpret_cast<float*>(a.workspace) : nullptr;
+    pl.C = p.C; pl.H = p.H; pl.W = p.W; pl.OH = p.OH; pl.OW = p.OW;
+    pl.tasks_per_plane = g.TP;
+    pl.tasks_padded = g.TPW;
+    pl.groups_per_row = p.OW / P;
+    pl.planes_per_pass = g.NP;
+    pl.passes_per_stage = PPS;
+    pl.n_compute_warps = g.NP * WPP;
+    pl.warps_per_plane = WPP;
+    pl.total_passes = g.total_passes;
+    pl.xplane_bytes = xpb;
+    pl.gplane_bytes = gpb;
+    pl.sf_bytes = sfb;
+    pl.fault = a.fault;
+    return true;
+}
+
+template <typename T, int K, int D, int S, int P, int MODE>
+int bwd_launch(const BwdArgs& a, cudaStream_t stream, int* launches) {
+    BwdPlan pl;
+    BwdGeometry g;
+    uint32_t smem = 0;
+    if (!make_bwd_plan<T, K, D, S, P>(a, pl, smem, g)) return kNotHandled;
+    if (a.gsf && !a.workspace) return DDF_B200_E_WORKSPACE;
+    auto kern = bwd_filters_kernel<T, K, D, S, P, MODE>;
+    static std::atomic<unsigned long long> opted_in{0};
+    const unsigned long long bit = 1ull << (a.device & 63);
+    if (!(opted_in.load(std::memory_order_acquire) & bit)) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kSmemBudget);
+        if (e != cudaSuccess) return (int)e;
+        opted_in.fetch_or(bit, std::memory_order_release);
+    }
+    const int threads = (pl.n_compute_warps + 1) * 32;
+    kern<<<g.grid, threads, smem, stream>>>(pl);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    ++*launches;
+    if (a.gsf) {
+        const long long n = (long long)a.p.k * a.p.k * a.p.OH * a.p.OW;
+        dim3 grid((unsigned)((n + 255) / 256 < 64 ? (n + 255) / 256 : 64),
+                  (unsigned)(a.p.B < 32768 ? a.p.B : 32768));
+        gsf_reduce_kernel<T><<<grid, 256, 0, stream>>>(reinterpret_cast<const float*>(a.workspace),
+                                                       reinterpret_cast<T*>(a.gsf), a.p.B, a.p.C,
+                                                       g.NP, n, g.total_passes, g.grid);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+        ++*launches;
+    }
+    return 0;
+}
+
+template <typename T>
+int bwd_dispatch(const BwdArgs& a, cudaStream_t stream, int* launches);
+
+}  // namespace ddf

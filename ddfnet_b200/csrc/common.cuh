@@ -88,14 +88,17 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false when the limit ran out (the caller records a
-// fault and leaves); never spins forever.
-constexpr uint32_t kWaitLimit = 1u << 22;
+// Bounded wait: gives up after about a second (kWaitCycles SM clocks).  Returns
+// false when the limit ran out (the caller records a fault and leaves); never
+// spins forever.
+constexpr long long kWaitCycles = 2000000000ll;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t it = 0; it < kWaitLimit; ++it) {
+    if (mbar_test(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
         if (mbar_test(bar, parity)) return true;
+        if (clock64() - t0 > kWaitCycles) return false;
     }
-    return false;
 }
 
 // Bulk asynchronous copy global -> shared (TMA, untiled).  dst, src 16-byte

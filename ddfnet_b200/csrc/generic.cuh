@@ -11,6 +11,20 @@
 
 namespace ddf {
 
+// Compensated (Neumaier) running sum, as the reference's kernels use for their
+// long sums (ddf/src/cuda/ddf_mul_cuda_kernel.cu:340-349, 406-414): the channel
+// sum of grad-sf and the pixel sum of grad-cf reach thousands of terms.
+template <typename A>
+struct CompSum {
+    A sum = 0, lost = 0;
+    __device__ __forceinline__ void add(A v) {
+        const A t = sum + v;
+        lost += (fabs(sum) >= fabs(v)) ? (sum - t) + v : (v - t) + sum;
+        sum = t;
+    }
+    __device__ __forceinline__ A value() const { return sum + lost; }
+};
+
 // out[b,c,y,x] = sum_t x[b,c,y*s+oi,x*s+oj] * w(cf[b,c,t], sf[b,t,y,x])
 // Replaces DDFForward (ddf/src/cuda/ddf_mul_cuda_kernel.cu:85-165).
 template <typename T, int MODE>
@@ -108,17 +122,17 @@ generic_grad_sf(const T* __restrict__ go, const T* __restrict__ x, const T* __re
         const long long b = idx / (opl * kk);
         const int iy = y * p.s + (t / p.k - r) * p.d;
         const int ix = xo * p.s + (t % p.k - r) * p.d;
-        A acc = 0;
+        CompSum<A> acc;
         if (iy >= 0 && iy < p.H && ix >= 0 && ix < p.W) {
             const T* gop = go + b * p.C * opl + (long long)y * p.OW + xo;
             const T* xp = x + b * p.C * ipl + (long long)iy * p.W + ix;
             const T* cfp = cf + b * p.C * kk + t;
             for (int c = 0; c < p.C; ++c) {
                 const A cfv = MODE == DDF_B200_MUL ? (A)Elem<T>::load(cfp + (long long)c * kk) : (A)1;
-                acc += Elem<T>::load(gop + c * opl) * Elem<T>::load(xp + c * ipl) * cfv;
+                acc.add(Elem<T>::load(gop + c * opl) * Elem<T>::load(xp + c * ipl) * cfv);
             }
         }
-        Elem<T>::store(gsf + idx, acc);
+        Elem<T>::store(gsf + idx, acc.value());
     }
 }
 
@@ -143,14 +157,15 @@ generic_grad_cf(const T* __restrict__ go, const T* __restrict__ x, const T* __re
         const T* sfb = sf + b * kk * (long long)opl;
         for (int t = 0; t < kk; ++t) {
             const int oi = (t / p.k - r) * p.d, oj = (t % p.k - r) * p.d;
-            A acc = 0;
+            CompSum<A> part;
             for (int q = threadIdx.x; q < opl; q += blockDim.x) {
                 const int y = q / p.OW, xo = q - y * p.OW;
                 const int iy = y * p.s + oi, ix = xo * p.s + oj;
                 if (iy < 0 || iy >= p.H || ix < 0 || ix >= p.W) continue;
                 const A sfv = MODE == DDF_B200_MUL ? (A)Elem<T>::load(sfb + (long long)t * opl + q) : (A)1;
-                acc += Elem<T>::load(gop + q) * Elem<T>::load(xp + (long long)iy * p.W + ix) * sfv;
+                part.add(Elem<T>::load(gop + q) * Elem<T>::load(xp + (long long)iy * p.W + ix) * sfv);
             }
+            A acc = part.value();
             for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = acc;
             __syncthreads();

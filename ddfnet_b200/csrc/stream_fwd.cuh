@@ -83,7 +83,9 @@ struct Geo {
     static constexpr int NRW = (NRE + EPW - 1) / EPW;    // halo words right of it
     static constexpr int OUTB = P * ES;
     static_assert(K == 3 || K == 5, "streaming kernel is instantiated for k = 3, 5");
-    static_assert(HALO <= P * S, "halo must fit in one neighbouring pixel group");
+    static constexpr int NLM = NLW > 0 ? NLW : 1;        // sizes of the halo mask arrays
+    static constexpr int NRM = NRW > 0 ? NRW : 1;
+    static_assert(!SUBWORD || HALO <= 1, "the element-wise path covers a halo of one only");
     static_assert(ES == 2 || ES == 4, "2- and 4-byte element types only");
 };
 
@@ -105,15 +107,15 @@ __device__ __forceinline__ void lds_vec(uint32_t a, uint32_t (&w)[NB / 4]) {
 // One input row of a thread's window, as floats.  rp = shared address of the
 // first main element (input column ox0*S of that row).
 template <typename T, typename G>
-__device__ __forceinline__ void load_row(uint32_t rp, uint32_t lmask, uint32_t rmask,
-                                         float (&xr)[G::NCOL]) {
+__device__ __forceinline__ void load_row(uint32_t rp, const uint32_t (&lmask)[G::NLM],
+                                         const uint32_t (&rmask)[G::NRM], float (&xr)[G::NCOL]) {
     if constexpr (G::SUBWORD) {
 #pragma unroll
         for (int c = 0; c < G::NCOL; ++c) {
             const int e = c - G::HALO;
             uint32_t w = lds16(rp + e * G::ES);
-            if (e < 0) w &= lmask;
-            if (e > 0) w &= rmask;
+            if (e < 0) w &= lmask[0];
+            if (e > 0) w &= rmask[0];
             xr[c] = Word<T>::get(w, 0);
         }
     } else {
@@ -121,10 +123,10 @@ __device__ __forceinline__ void load_row(uint32_t rp, uint32_t lmask, uint32_t r
         uint32_t mw[G::MAINW];
         uint32_t rw[G::NRW > 0 ? G::NRW : 1];
 #pragma unroll
-        for (int a = 0; a < G::NLW; ++a) lw[a] = lds32(rp - 4 * (G::NLW - a)) & lmask;
+        for (int a = 0; a < G::NLW; ++a) lw[a] = lds32(rp - 4 * (G::NLW - a)) & lmask[a];
         lds_vec<G::MAINB>(rp, mw);
 #pragma unroll
-        for (int a = 0; a < G::NRW; ++a) rw[a] = lds32(rp + G::MAINB + 4 * a) & rmask;
+        for (int a = 0; a < G::NRW; ++a) rw[a] = lds32(rp + G::MAINB + 4 * a) & rmask[a];
 #pragma unroll
         for (int c = 0; c < G::NCOL; ++c) {
             const int e = c - G::HALO;
@@ -138,6 +140,29 @@ __device__ __forceinline__ void load_row(uint32_t rp, uint32_t lmask, uint32_t r
                 xr[c] = Word<T>::get(rw[idx / G::EPW], idx % G::EPW);
             }
         }
+    }
+}
+
+// Per-thread halo masks: all ones where the halo word lies inside the row, zero
+// where it hangs over the left / right edge of the plane (those reads land on
+// neighbouring data in shared memory and are cleared by the AND).  A word is
+// never half inside: its first column is a multiple of the elements per word
+// and the row width is even whenever a word holds two elements.
+template <typename G>
+__device__ __forceinline__ void halo_masks(int ox0, int S, int W, uint32_t (&lmask)[G::NLM],
+                                           uint32_t (&rmask)[G::NRM]) {
+    if constexpr (G::SUBWORD) {
+        lmask[0] = ox0 > 0 ? 0xffffffffu : 0u;
+        rmask[0] = ox0 + 1 < W ? 0xffffffffu : 0u;
+    } else {
+        lmask[0] = 0u;
+        rmask[0] = 0u;
+#pragma unroll
+        for (int a = 0; a < G::NLW; ++a)
+            lmask[a] = (ox0 * S - (G::NLW - a) * G::EPW >= 0) ? 0xffffffffu : 0u;
+#pragma unroll
+        for (int a = 0; a < G::NRW; ++a)
+            rmask[a] = (ox0 * S + G::MAINN + a * G::EPW + (G::EPW - 1) <= W - 1) ? 0xffffffffu : 0u;
     }
 }
 
@@ -231,23 +256,22 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
         int issue_i = 0, conv_j = 0, seg_k = 0;
         long long seg_b = plane_lo / pl.C;
         long long seg_plane = plane_lo;  // first plane of the next sample segment
-        uint32_t idle = 0;
+        long long idle_since = -1;
         bool gave_up = false;
-        while (conv_j < my_stages) {
+        // Runs until every stage has been converted AND the spatial filter of every
+        // sample that starts inside this CTA's run has been requested.
+        while (conv_j < my_stages || seg_plane < plane_hi) {
             bool progress = false;
-            if (issue_i < my_stages) {
-                const long long st_first = plane_lo + (long long)issue_i * stage_planes;
-                long long st_end = st_first + stage_planes;
-                if (st_end > plane_hi) st_end = plane_hi;
-                // A new sample begins inside this stage: its spatial filter is fetched
-                // as soon as the buffer is free, i.e. once every compute warp has copied
-                // the previous sample's values into registers.  Stage copies never wait
-                // for that (the compute warps need the stage to get that far).
-                const bool want_sf = seg_plane < st_end;
-                const bool free_buf =
-                    want_sf &&
-                    (seg_k == 0 || warp_test(bar_sf_empty, (uint32_t)((seg_k - 1) & 1), lane));
-                if (free_buf) {
+            // (1) Spatial filter of the next sample: requested once its first plane lies
+            // within the stages issued so far or the one about to be issued, and the
+            // buffer is free, i.e. every compute warp has copied the previous sample's
+            // values into registers.
+            {
+                const int ahead = issue_i + 1 < my_stages ? issue_i + 1 : my_stages;
+                long long horizon = plane_lo + (long long)ahead * stage_planes;
+                if (horizon > plane_hi) horizon = plane_hi;
+                if (seg_plane < horizon &&
+                    (seg_k == 0 || warp_test(bar_sf_empty, (uint32_t)((seg_k - 1) & 1), lane))) {
                     if (lane == 0) {
                         const unsigned long long g0 = (unsigned long long)seg_b * pl.sf_bytes;
                         const unsigned long long a0 = g0 & ~15ull;
@@ -260,28 +284,33 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                     ++seg_b;
                     seg_plane = seg_b * pl.C;
                     progress = true;
-                } else {
-                    const int slot = issue_i % NST;
-                    const bool free_slot =
-                        issue_i < NST ||
-                        warp_test(BAR_EMPTY(slot), (uint32_t)((issue_i / NST - 1) & 1), lane);
-                    if (free_slot) {
-                        if (lane == 0) {
-                            const unsigned long long g0 = (unsigned long long)st_first * pl.plane_bytes;
-                            const unsigned long long g1 = (unsigned long long)st_end * pl.plane_bytes;
-                            const unsigned long long a0 = g0 & ~15ull, a1 = (g1 + 15ull) & ~15ull;
-                            const unsigned long long c0 = (unsigned long long)st_first * (KK * ES);
-                            const unsigned long long c1 = (unsigned long long)st_end * (KK * ES);
-                            const unsigned long long ca0 = c0 & ~15ull, ca1 = (c1 + 15ull) & ~15ull;
-                            mbar_arrive_expect_tx(BAR_FULL(slot), (uint32_t)((a1 - a0) + (ca1 - ca0)));
-                            bulk_g2s(STAGE_BASE(slot) + 32u, (const char*)pl.in + a0,
-                                     (uint32_t)(a1 - a0), BAR_FULL(slot));
-                            bulk_g2s(STAGE_BASE(slot) + pl.off_rawcf, (const char*)pl.cf + ca0,
-                                     (uint32_t)(ca1 - ca0), BAR_FULL(slot));
-                        }
-                        ++issue_i;
-                        progress = true;
+                }
+            }
+            // (2) Next stage, as soon as its slot has been released.
+            if (issue_i < my_stages) {
+                const int slot = issue_i % NST;
+                const bool free_slot =
+                    issue_i < NST ||
+                    warp_test(BAR_EMPTY(slot), (uint32_t)((issue_i / NST - 1) & 1), lane);
+                if (free_slot) {
+                    const long long st_first = plane_lo + (long long)issue_i * stage_planes;
+                    long long st_end = st_first + stage_planes;
+                    if (st_end > plane_hi) st_end = plane_hi;
+                    if (lane == 0) {
+                        const unsigned long long g0 = (unsigned long long)st_first * pl.plane_bytes;
+                        const unsigned long long g1 = (unsigned long long)st_end * pl.plane_bytes;
+                        const unsigned long long a0 = g0 & ~15ull, a1 = (g1 + 15ull) & ~15ull;
+                        const unsigned long long c0 = (unsigned long long)st_first * (KK * ES);
+                        const unsigned long long c1 = (unsigned long long)st_end * (KK * ES);
+                        const unsigned long long ca0 = c0 & ~15ull, ca1 = (c1 + 15ull) & ~15ull;
+                        mbar_arrive_expect_tx(BAR_FULL(slot), (uint32_t)((a1 - a0) + (ca1 - ca0)));
+                        bulk_g2s(STAGE_BASE(slot) + 32u, (const char*)pl.in + a0,
+                                 (uint32_t)(a1 - a0), BAR_FULL(slot));
+                        bulk_g2s(STAGE_BASE(slot) + pl.off_rawcf, (const char*)pl.cf + ca0,
+                                 (uint32_t)(ca1 - ca0), BAR_FULL(slot));
                     }
+                    ++issue_i;
+                    progress = true;
                 }
             }
             if (conv_j < issue_i) {
@@ -308,8 +337,10 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                 }
             }
             if (progress) {
-                idle = 0;
-            } else if (++idle > kWaitLimit) {
+                idle_since = -1;
+            } else if (idle_since < 0) {
+                idle_since = clock64();
+            } else if (clock64() - idle_since > kWaitCycles) {
                 gave_up = true;
                 break;
             }
@@ -345,8 +376,8 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
         rowok[i] = iy >= 0 && iy < pl.H;
         rowoff[i] = (uint32_t)((iy * pl.W + ox0 * S) * ES);
     }
-    const uint32_t lmask = ox0 > 0 ? 0xffffffffu : 0u;
-    const uint32_t rmask = (ox0 + P < pl.OW) ? 0xffffffffu : 0u;
+    uint32_t lmask[G::NLM], rmask[G::NRM];
+    halo_masks<G>(ox0, S, pl.W, lmask, rmask);
     const uint32_t zero_row = sbase + pl.off_zero + 64u;
 
     float sfr[KK][P];

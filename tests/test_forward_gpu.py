@@ -45,25 +45,28 @@ def test_generic_forward(shape, dt):
 
 
 # ------------------------------------------------------------------ streaming kernel
+# (The streaming kernels take a tensor only if its byte size is a multiple of 16:
+# the batch sizes below are chosen accordingly; other sizes fall back to the
+# generic kernel, which test_auto_falls_back covers.)
 # B, C, H, W, k, d, s -- every (k, d, s, P) instantiation, plane runs that cross
 # sample boundaries inside a CTA, several samples inside one stage (small C),
 # fewer plane groups than SMs, and widths for each pixels-per-thread choice.
 STREAM = [
     (4, 16, 56, 56, 3, 1, 1),    # P = 8
     (3, 64, 28, 28, 3, 1, 1),    # P = 4, two planes per pass
-    (5, 32, 14, 14, 3, 1, 1),    # P = 2
-    (7, 64, 7, 7, 3, 1, 1),      # P = 1 (sub-word path for 2-byte types)
+    (8, 32, 14, 14, 3, 1, 1),    # P = 2
+    (8, 64, 7, 7, 3, 1, 1),      # P = 1 (sub-word path for 2-byte types)
     (40, 8, 7, 7, 3, 1, 1),      # C = planes per pass: a new sample every pass
     (300, 2, 14, 14, 3, 1, 1),   # more samples than CTAs, two planes per sample
     (3, 32, 56, 56, 3, 1, 2),    # stride 2, P = 4
-    (3, 32, 28, 28, 3, 1, 2),    # stride 2, P = 2
-    (3, 64, 14, 14, 3, 1, 2),    # stride 2, P = 1
+    (8, 32, 28, 28, 3, 1, 2),    # stride 2, P = 2
+    (8, 64, 14, 14, 3, 1, 2),    # stride 2, P = 1
     (2, 16, 57, 56, 3, 1, 2),    # odd height at stride 2 (floor output size)
     (3, 16, 56, 56, 3, 2, 1),    # dilation 2, P = 8
     (3, 32, 28, 28, 3, 2, 1),
-    (3, 32, 14, 14, 3, 2, 1),
+    (8, 32, 14, 14, 3, 2, 1),
     (3, 32, 28, 28, 5, 1, 1),    # k = 5
-    (3, 32, 14, 14, 5, 1, 1),
+    (8, 32, 14, 14, 5, 1, 1),
     (3, 32, 28, 28, 5, 2, 1),
     (2, 24, 20, 24, 3, 1, 1),    # non-square, H*W/8 = 60 tasks, 6 planes per pass
     (1, 8, 40, 64, 3, 1, 1),     # wide plane, single sample
@@ -81,6 +84,18 @@ def test_stream_forward(shape, dt):
         out = _run(x, cf, sf, k, d, s, m, "f")
         check_close(out, oracle_forward(x, cf, sf, k, d, s, m), dtype, f"stream {shape} {dt} {m}")
     _no_fault()
+
+
+def test_auto_falls_back():
+    """Sizes the streaming kernels decline (a tensor whose byte size is not a
+    multiple of 16, here sf) are served by the generic kernel under AUTO and refused
+    under 'f'."""
+    from ddfnet_b200._lib import DDFError
+    x, cf, sf = make_inputs(5, 32, 14, 14, 3, 1, torch.bfloat16, seed=3, with_go=False)
+    with pytest.raises(DDFError):
+        _run(x, cf, sf, 3, 1, 1, "mul", "f")
+    check_close(_run(x, cf, sf, 3, 1, 1, "mul", ""), oracle_forward(x, cf, sf, 3, 1, 1, "mul"),
+                torch.bfloat16, "auto fallback")
 
 
 def test_stream_rejects_what_it_cannot_do():
@@ -143,7 +158,11 @@ def test_config2_full_size(case, dt):
         out = _run(x, cf, sf, 3, 1, s, m)
         check_close(out, oracle_forward(x, cf, sf, 3, 1, s, m), dtype, f"config 2 {case} {dt} {m}")
         out2 = _run(x * 2, cf, sf, 3, 1, s, m)
-        assert torch.equal(out2, out * 2)
+        if dtype == torch.float16:   # float16 results below 2**-14 are subnormal: not scale-exact
+            keep = out.abs() > 1e-3
+            assert torch.equal(out2[keep], (out * 2)[keep])
+        else:
+            assert torch.equal(out2, out * 2)
     _no_fault()
 
 
