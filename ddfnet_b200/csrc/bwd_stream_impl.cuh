@@ -80,16 +80,24 @@ __device__ __forceinline__ void butterfly_reduce(float (&v)[GROUP], int lane) {
     }
 }
 
-// Which of the GROUP values ends up in this lane (-1: none).
+// Which of the GROUP values ends up in this lane (-1: none).  Mirrors the
+// splits butterfly_reduce makes: every level halves the (compile-time) array
+// length n; `cnt` is how many of this lane's array entries are real values.
 template <int GROUP>
 __device__ __forceinline__ int butterfly_slot(int lane) {
-    int a = 0, b = GROUP;
+    int n = GROUP, first = 0, cnt = GROUP;
 #pragma unroll
     for (int lvl = 0; lvl < 5; ++lvl) {
-        const int lo = (b - a + 1) / 2;
-        if (lane & (16 >> lvl)) a += lo; else b = a + lo;
+        const int lo = (n + 1) / 2;
+        if (lane & (16 >> lvl)) {
+            first += lo;
+            cnt = cnt > lo ? cnt - lo : 0;
+        } else {
+            cnt = cnt < lo ? cnt : lo;
+        }
+        n = lo;
     }
-    return a < b ? a : -1;
+    return cnt > 0 ? first : -1;
 }
 
 template <typename T, int K, int D, int S, int P, int MODE>
