@@ -405,6 +405,29 @@ def run_model(args, rank, world, local_rank):
             "logits_finite": bool(torch.isfinite(logits).all()), "logits_shape": list(logits.shape)}))
 
 
+def run_ncu_case(spec):
+    from ddfnet_b200 import ddf
+    parts = spec.split(",")
+    C, H, s = int(parts[0]), int(parts[1]), int(parts[2])
+    dtype = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[parts[3]]
+    mode = parts[4]
+    backward = len(parts) > 5 and parts[5] == "backward"
+    dev = torch.device("cuda:0")
+    B = 64 if backward else BATCH
+    sets = [make_case(C, H, s, dtype, B, dev, 7 + i) for i in range(3)]
+    if backward:
+        go = torch.randn(B, C, H // s, H // s, device=dev).to(dtype)
+        for i in range(6):
+            xs = [t.detach().requires_grad_() for t in sets[i % 3]]
+            ddf(*xs, K, D, s, mode).backward(go)
+    else:
+        with torch.no_grad():
+            for i in range(6):
+                ddf(*sets[i % 3], K, D, s, mode)
+    torch.cuda.synchronize()
+    print("ok")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -414,6 +437,9 @@ def main():
     ap.add_argument("--workload", default="op", choices=["op", "model"])
     ap.add_argument("--model", default="ddf_mul_resnet50", choices=sorted(MODEL_CFG))
     ap.add_argument("--detail", default=None, help="also write the JSON, indented, to this file")
+    ap.add_argument("--ncu-case", default=None, metavar="C,H,stride,dtype,combine[,backward]",
+                    help="profiling aid: run only this case, 6 launches over 3 rotating buffer "
+                         "sets at B=128 (B=64 for backward), print nothing but 'ok'")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -422,6 +448,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.ncu_case:
+        run_ncu_case(args.ncu_case)
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the op)")
