@@ -21,7 +21,7 @@ VARIANT_AUTO, VARIANT_GENERIC, VARIANT_STREAM = 0, 1, 2
 SYMBOLS = (
     "ddf_b200_version", "ddf_b200_strerror", "ddf_b200_forward", "ddf_b200_plan",
     "ddf_b200_backward_workspace", "ddf_b200_backward", "ddf_b200_take_fault",
-    "ddf_b200_launch_count",
+    "ddf_b200_launch_count", "ddf_b200_backward_noalloc", "ddf_b200_backward_noalloc_limit",
 )
 
 
@@ -54,6 +54,10 @@ def load() -> ctypes.CDLL:
         L.ddf_b200_backward_workspace.argtypes = [i] * 10
         L.ddf_b200_backward.restype = i
         L.ddf_b200_backward.argtypes = [vp] * 7 + [vp, sz] + [i] * 10 + [vp]
+        L.ddf_b200_backward_noalloc.restype = i
+        L.ddf_b200_backward_noalloc.argtypes = [vp] * 7 + [i] * 9 + [vp]
+        L.ddf_b200_backward_noalloc_limit.restype = sz
+        L.ddf_b200_backward_noalloc_limit.argtypes = []
         L.ddf_b200_take_fault.restype = i
         L.ddf_b200_take_fault.argtypes = []
         L.ddf_b200_launch_count.restype = ctypes.c_ulonglong

@@ -51,6 +51,17 @@ static int device_info(DeviceInfo*& out) {
     return 0;
 }
 
+// Per-device facts for other translation units of this library.
+int device_facts(int* sm_count, int** fault, int* index) {
+    DeviceInfo* di = nullptr;
+    const int rc = device_info(di);
+    if (rc) return rc;
+    *sm_count = di->sm_count;
+    *fault = di->fault;
+    *index = di->index;
+    return 0;
+}
+
 static int check_problem(int B, int C, int H, int W, int k, int d, int s, int combine, int dtype,
                          int variant, Problem& p) {
     if (B < 1 || C < 1 || H < 1 || W < 1) return DDF_B200_E_SHAPE;
@@ -228,6 +239,9 @@ const char* ddf_b200_strerror(int status) {
         case DDF_B200_E_WORKSPACE: return "ddf_b200: workspace is NULL or too small";
         case DDF_B200_E_TOO_LARGE: return "ddf_b200: problem exceeds the kernels' index ranges";
         case DDF_B200_E_DEVICE: return "ddf_b200: current device is not an sm_100 GPU";
+        case DDF_B200_E_SCRATCH_LIMIT:
+            return "ddf_b200: this problem needs more scratch than ddf_b200_backward_noalloc's "
+                   "built-in 16 MiB array; use ddf_b200_backward with a caller-provided workspace";
         default: break;
     }
     if (status > 0) return cudaGetErrorString((cudaError_t)status);

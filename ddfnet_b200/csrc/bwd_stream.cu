@@ -54,3 +54,95 @@ int bwd_stream_filters(const Problem& p, const void* go, const void* x, const vo
 }
 
 }  // namespace ddf
+
+// ---------------------------------------------------------------------------
+// Backward for callers that cannot allocate device memory.
+//
+// The filter-gradient kernel needs scratch for its float partial sums.  The
+// regular entry point takes that scratch from the caller; some callers have no
+// way to provide it: code running under a fixed memory plan or inside another
+// framework's allocator-free region (a serving runtime that sized its arena at
+// start-up, a plugin called where cudaMalloc is forbidden because it would
+// synchronise the device or fragment a tightly packed pool).  For them the
+// scratch lives in this library's own image: a file-scope device array of
+// kStaticScratchBytes that every GPU loading the library holds until exit.
+//
+// In host code the array's NAME is only a host-side handle, not a device
+// address (a kernel handed it would fault, or scribble over host memory where
+// the GPU can reach it).  The device address is obtained once per device, with
+// that device current, by cudaGetSymbolAddress, and that pointer is what the
+// kernels receive.
+// ---------------------------------------------------------------------------
+namespace ddf {
+
+constexpr size_t kStaticScratchBytes = 16u << 20;  // 16 MiB per GPU
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+static void* g_static_scratch_ptr[64] = {nullptr};
+
+// Device address of the static scratch on the current device (set up on first use).
+static int static_scratch_address(int device, void** out) {
+    if (device < 0 || device >= 64) return DDF_B200_E_DEVICE;
+    if (g_static_scratch_ptr[device] == nullptr) {
+        void* ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        g_static_scratch_ptr[device] = ptr;
+    }
+    *out = g_static_scratch_ptr[device];
+    return 0;
+}
+
+}  // namespace ddf
+
+extern "C" {
+
+size_t ddf_b200_backward_noalloc_limit(void) { return ddf::kStaticScratchBytes; }
+
+int ddf_b200_backward_noalloc(const void* go, const void* x, const void* cf, const void* sf,
+                              void* gx, void* gcf, void* gsf, int B, int C, int H, int W, int k,
+                              int d, int s, int combine, int dtype, void* stream) {
+    using namespace ddf;
+    // Argument checks only: the regular entry point with no gradient requested
+    // validates everything and launches nothing.
+    int rc = ddf_b200_backward(go, x, cf, sf, nullptr, nullptr, nullptr, nullptr, 0, B, C, H, W, k, d,
+                               s, combine, dtype, DDF_B200_VARIANT_AUTO, stream);
+    if (rc) return rc;
+
+    Problem p;
+    p.B = B; p.C = C; p.H = H; p.W = W; p.OH = H / s; p.OW = W / s;
+    p.k = k; p.d = d; p.s = s; p.combine = combine; p.dtype = dtype;
+    int sm_count = 0, index = 0;
+    int* fault = nullptr;
+    rc = device_facts(&sm_count, &fault, &index);
+    if (rc) return rc;
+
+    // Refuse before anything is launched if the filter gradients would need more
+    // scratch than the built-in array holds.
+    const bool streaming = (gcf || gsf) && bwd_stream_supported(p);
+    if (streaming && bwd_stream_workspace(p, sm_count) > kStaticScratchBytes)
+        return DDF_B200_E_SCRATCH_LIMIT;
+
+    // grad-x needs no scratch: regular entry point, filter gradients not requested.
+    if (gx) {
+        rc = ddf_b200_backward(go, x, cf, sf, gx, nullptr, nullptr, nullptr, 0, B, C, H, W, k, d, s,
+                               combine, dtype, DDF_B200_VARIANT_AUTO, stream);
+        if (rc) return rc;
+    }
+    if (!gcf && !gsf) return 0;
+
+    if (streaming) {
+        void* scratch = nullptr;
+        rc = static_scratch_address(index, &scratch);
+        if (rc) return rc;
+        int launches = 0;
+        rc = bwd_stream_filters(p, go, x, cf, sf, gcf, gsf, scratch, sm_count, fault, index,
+                                reinterpret_cast<cudaStream_t>(stream), &launches);
+        if (rc != kNotHandled) return rc;
+    }
+    // Outside the streaming kernel's range: the generic kernels use no scratch at all.
+    return ddf_b200_backward(go, x, cf, sf, nullptr, gcf, gsf, nullptr, 0, B, C, H, W, k, d, s,
+                             combine, dtype, DDF_B200_VARIANT_GENERIC, stream);
+}
+
+}  // extern "C"

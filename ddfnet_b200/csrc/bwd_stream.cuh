@@ -21,4 +21,7 @@ int bwd_stream_filters(const Problem& p, const void* go, const void* x, const vo
                        const void* sf, void* gcf, void* gsf, void* workspace, int sm_count,
                        int* fault, int device, cudaStream_t st, int* launches);
 
+// Defined in abi.cu: SM count, fault word and index of the current device.
+int device_facts(int* sm_count, int** fault, int* index);
+
 }  // namespace ddf

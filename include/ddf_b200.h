@@ -62,6 +62,8 @@ extern "C" {
 #define DDF_B200_E_WORKSPACE (-8)   /* workspace NULL or smaller than required         */
 #define DDF_B200_E_TOO_LARGE (-9)   /* an index would not fit the kernels' ranges      */
 #define DDF_B200_E_DEVICE (-10)     /* no usable CUDA device / not an sm_100 device    */
+#define DDF_B200_E_SCRATCH_LIMIT (-11) /* ddf_b200_backward_noalloc: problem needs more
+                                          scratch than the built-in array holds          */
 
 /* Library version: major*10000 + minor*100 + patch. */
 int ddf_b200_version(void);
@@ -114,6 +116,41 @@ int ddf_b200_backward(const void* go, const void* x, const void* cf, const void*
                       void* workspace, size_t workspace_bytes,
                       int B, int C, int H, int W, int k, int d, int s,
                       int combine, int dtype, int variant, void* stream);
+
+/*
+ * Backward for callers that cannot allocate device memory: same inputs, outputs
+ * and results as ddf_b200_backward, but no workspace argument.  It has no
+ * counterpart in the reference (whose Python wrapper allocates six tensors per
+ * call, ddf/ddf.py:106-111).
+ *
+ * Who needs it: hosts that must not call cudaMalloc on this path -- a serving
+ * runtime whose device arena was sized at start-up, a plugin invoked where an
+ * allocation would synchronise the device or disturb a packed memory pool, a
+ * caller with no allocator at hand at all.  The scratch the filter-gradient
+ * kernel needs is a fixed array inside the library image instead:
+ * ddf_b200_backward_noalloc_limit() bytes (16 MiB), held by every GPU that
+ * loads the library until the process exits.
+ *
+ *   - Problems whose scratch need (what ddf_b200_backward_workspace reports)
+ *     exceeds that limit are refused with DDF_B200_E_SCRATCH_LIMIT before
+ *     anything is launched.
+ *   - The call itself performs no cudaMalloc / cudaFree and uses no allocating
+ *     library routine.
+ *   - The first call on each device looks up the array's device address (one
+ *     cudaGetSymbolAddress, with that device current).  Make that first call
+ *     before starting any stream capture on the device.
+ *   - All calls on a device share the one array and it keeps whatever the last
+ *     call left in it.  The kernels write every scratch slot they later read, so
+ *     nothing needs clearing between calls; but two calls whose kernels overlap
+ *     on the GPU (different streams, no dependency) race on it -- serialise them.
+ */
+int ddf_b200_backward_noalloc(const void* go, const void* x, const void* cf, const void* sf,
+                              void* gx, void* gcf, void* gsf,
+                              int B, int C, int H, int W, int k, int d, int s,
+                              int combine, int dtype, void* stream);
+
+/* Size in bytes of the built-in scratch array used by ddf_b200_backward_noalloc. */
+size_t ddf_b200_backward_noalloc_limit(void);
 
 /*
  * Reads and clears the per-device fault word that the streaming kernels set
