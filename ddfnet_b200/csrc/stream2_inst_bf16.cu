@@ -1,0 +1,3 @@
+// Second-generation streaming kernel instantiations for __nv_bfloat16 elements.
+#define DDF_INST_T __nv_bfloat16
+#include "stream2_inst.inc"
