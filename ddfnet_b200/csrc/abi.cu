@@ -7,9 +7,6 @@
 #include "common.cuh"
 #include "generic.cuh"
 #include "stream_fwd.cuh"
-#include "stream_v2.cuh"
-
-#include <cstdlib>
 
 namespace ddf {
 
@@ -201,33 +198,8 @@ static int stream_pixels(const Problem& p, bool bwdx) {
     return 0;
 }
 
-// The second-generation kernel is tried first where it applies (k = 3, d = 1);
-// DDF_B200_V2=0 in the environment keeps to the first generation (A/B timing).
-static bool v2_enabled() {
-    static const int on = [] {
-        const char* e = std::getenv("DDF_B200_V2");
-        return (e && e[0] == '0') ? 0 : 1;
-    }();
-    return on != 0;
-}
-
 static int run_stream(const StreamArgs& a, cudaStream_t st) {
-    int rc = kNotHandled;
-    if (v2_enabled()) {
-        const int L = v2_segment(a.p, a.bwdx);
-        if (L > 0) {
-            StreamArgs a2 = a;
-            a2.P = L;
-            switch (a.p.dtype) {
-                case DDF_B200_F32: rc = stream2_dispatch<float>(a2, st); break;
-                case DDF_B200_F16: rc = stream2_dispatch<__half>(a2, st); break;
-                case DDF_B200_BF16: rc = stream2_dispatch<__nv_bfloat16>(a2, st); break;
-                default: rc = kNotHandled;
-            }
-            if (rc == 0) g_launches.fetch_add(1, std::memory_order_relaxed);
-            if (rc != kNotHandled) return rc;
-        }
-    }
+    int rc;
     switch (a.p.dtype) {
         case DDF_B200_F32: rc = stream_dispatch<float>(a, st); break;
         case DDF_B200_F16: rc = stream_dispatch<__half>(a, st); break;

@@ -339,9 +339,11 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
             for (int pp = 0; pp < P; ++pp) gsf[t][pp] = 0.f;
     };
 
+    int slot = -1;
+    uint32_t ph = 1;  // becomes slot 0, phase 0 on the first stage; no division per stage
     for (int st = 0; st < my_stages; ++st) {
-        const int slot = st % NST;
-        const uint32_t ph = (uint32_t)((st / NST) & 1);
+        if (++slot == NST) slot = 0;
+        if (slot == 0) ph ^= 1u;
         if (!mbar_wait(BAR_FULL(slot), ph) || !mbar_wait(BAR_READY(slot), ph)) {
             atomicCAS(pl.fault, 0, (int)kFaultConsumerFull);
             return;

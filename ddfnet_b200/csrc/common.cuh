@@ -76,7 +76,8 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
-// One non-blocking probe: true when the phase with this parity has completed.
+// One probe: true when the phase with this parity has completed.  Used by the
+// service warps' polling loops, which must stay responsive to several barriers.
 __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -88,6 +89,20 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same probe for threads that have nothing else to do: the hardware may park
+// the thread for up to the hinted time (ns) before answering "not yet", which
+// keeps waiting warps from burning issue slots in a spin loop.
+__device__ __forceinline__ bool mbar_test_parked(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(2000u)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after about a second (kWaitCycles SM clocks).  Returns
 // false when the limit ran out (the caller records a fault and leaves); never
 // spins forever.
@@ -96,7 +111,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (mbar_test(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
-        if (mbar_test(bar, parity)) return true;
+        if (mbar_test_parked(bar, parity)) return true;
         if (clock64() - t0 > kWaitCycles) return false;
     }
 }
@@ -132,6 +147,11 @@ __device__ __forceinline__ void lds128(uint32_t a, uint32_t& x, uint32_t& y, uin
                  : "r"(a));
 }
 __device__ __forceinline__ float ldsf(uint32_t a) { return __uint_as_float(lds32(a)); }
+__device__ __forceinline__ unsigned long long lds64_pair(uint32_t a) {
+    unsigned long long v;
+    asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(a));
+    return v;
+}
 __device__ __forceinline__ void sts32(uint32_t a, uint32_t v) {
     asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
 }

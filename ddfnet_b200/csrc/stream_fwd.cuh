@@ -328,7 +328,8 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                         float v;
                         if constexpr (ES == 4) v = ldsf(src + 4u * e);
                         else v = Word<T>::get(lds16(src + 2u * e), 0);
-                        sts32(dst + 4u * e, __float_as_uint(v));
+                        sts32(dst + 8u * e, __float_as_uint(v));      // (cf, cf): ready for
+                        sts32(dst + 8u * e + 4u, __float_as_uint(v)); // the two-wide multiply
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(BAR_READY(slot));
@@ -380,11 +381,25 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
     halo_masks<G>(ox0, S, pl.W, lmask, rmask);
     const uint32_t zero_row = sbase + pl.off_zero + 64u;
 
-    float sfr[KK][P];
+    // Spatial-filter values of this thread's pixels.  With packed arithmetic they are
+    // kept as (pixel q, pixel q + P/2) pairs, the operand layout of mul/fma.f32x2.
+    constexpr bool PK = PACK && P >= 2;
+    float sfr[PK ? 1 : KK][PK ? 1 : P];
+    unsigned long long sf2[PK ? KK : 1][PK ? P / 2 : 1];
+    auto set_sf = [&](int t, int pp, float v) {
+        if constexpr (PK) {
+            float lo, hi;
+            f2_unpack(sf2[t][pp % (P / 2)], lo, hi);
+            if (pp < P / 2) lo = v; else hi = v;
+            sf2[t][pp % (P / 2)] = f2_pack(lo, hi);
+        } else {
+            sfr[t][pp] = v;
+        }
+    };
 #pragma unroll
     for (int t = 0; t < KK; ++t)
 #pragma unroll
-        for (int pp = 0; pp < P; ++pp) sfr[t][pp] = 0.f;
+        for (int pp = 0; pp < P; ++pp) set_sf(t, pp, 0.f);
 
     long long b = plane_lo / pl.C;
     int c_in_b = (int)(plane_lo - b * pl.C);
@@ -394,9 +409,11 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
     T* outp = reinterpret_cast<T*>(pl.out) + (plane_lo + pip) * out_plane + (long long)oy * pl.OW + ox0;
     const long long out_step = (long long)NP * out_plane;
 
+    int slot = -1;
+    uint32_t ph = 1;  // becomes slot 0, phase 0 on the first stage; no division per stage
     for (int st = 0; st < my_stages; ++st) {
-        const int slot = st % NST;
-        const uint32_t ph = (uint32_t)((st / NST) & 1);
+        if (++slot == NST) slot = 0;
+        if (slot == 0) ph ^= 1u;
         if (!mbar_wait(BAR_FULL(slot), ph) || !mbar_wait(BAR_READY(slot), ph)) {
             atomicCAS(pl.fault, 0, (int)kFaultConsumerFull);
             return;
@@ -406,7 +423,7 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
         const unsigned long long st_first_plane = (unsigned long long)plane_lo + (unsigned long long)first_pass * NP;
         const uint32_t xoff = (uint32_t)((st_first_plane * pl.plane_bytes) & 15ull);
         uint32_t plane_s = STAGE_BASE(slot) + 32u + xoff + (uint32_t)pip * pl.plane_bytes;
-        uint32_t cfc_s = sbase + pl.off_cfc + (uint32_t)slot * pl.cfc_stride + (uint32_t)pip * (KK * 4);
+        uint32_t cfc_s = sbase + pl.off_cfc + (uint32_t)slot * pl.cfc_stride + (uint32_t)pip * (KK * 8);
 
         for (int q = 0; q < npass; ++q) {
             if (need_sf) {
@@ -421,13 +438,13 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                     for (int t = 0; t < KK; ++t) {
                         const uint32_t a = sfs + (uint32_t)(((t * pl.OH + oy) * pl.OW + ox0) * ES);
                         if constexpr (G::OUTB < 4) {
-                            sfr[t][0] = Word<T>::get(lds16(a), 0);
+                            set_sf(t, 0, Word<T>::get(lds16(a), 0));
                         } else {
                             uint32_t w[G::OUTB / 4];
                             lds_vec<G::OUTB>(a, w);
 #pragma unroll
                             for (int pp = 0; pp < P; ++pp)
-                                sfr[t][pp] = Word<T>::get(w[pp / G::EPW], pp % G::EPW);
+                                set_sf(t, pp, Word<T>::get(w[pp / G::EPW], pp % G::EPW));
                         }
                     }
                 } else {
@@ -448,7 +465,7 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                                     if constexpr (ES == 4) v = ldsf(a);
                                     else v = Word<T>::get(lds16(a), 0);
                                 }
-                                sfr[i * K + j][pp] = v;
+                                set_sf(i * K + j, pp, v);
                             }
                         }
                     }
@@ -459,13 +476,15 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                 need_sf = false;
             }
 
-            float cfv[KK];
+            float acc[PK ? 1 : P];
+            unsigned long long acc2[PK ? P / 2 : 1];
+            if constexpr (PK) {
 #pragma unroll
-            for (int t = 0; t < KK; ++t) cfv[t] = ldsf(cfc_s + 4u * t);
-
-            float acc[P];
+                for (int q2 = 0; q2 < P / 2; ++q2) acc2[q2] = 0ull;
+            } else {
 #pragma unroll
-            for (int pp = 0; pp < P; ++pp) acc[pp] = 0.f;
+                for (int pp = 0; pp < P; ++pp) acc[pp] = 0.f;
+            }
 
 #pragma unroll
             for (int i = 0; i < K; ++i) {
@@ -475,28 +494,36 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
 #pragma unroll
                 for (int j = 0; j < K; ++j) {
                     const int t = i * K + j;
-                    const float c = cfv[BWDX ? (KK - 1 - t) : t];
-                    if constexpr (PACK && P >= 2) {
+                    const uint32_t ca = cfc_s + 8u * (uint32_t)(BWDX ? (KK - 1 - t) : t);
+                    if constexpr (PK) {
+                        const unsigned long long c2 = lds64_pair(ca);
 #pragma unroll
                         for (int q2 = 0; q2 < P / 2; ++q2) {
-                            const float w0 = combine_w<MODE, float>(c, sfr[t][q2]);
-                            const float w1 = combine_w<MODE, float>(c, sfr[t][q2 + P / 2]);
-                            unsigned long long a2 = f2_pack(acc[q2], acc[q2 + P / 2]);
-                            a2 = f2_fma(f2_pack(w0, w1),
-                                        f2_pack(xr[q2 * S + j * D], xr[(q2 + P / 2) * S + j * D]), a2);
-                            f2_unpack(a2, acc[q2], acc[q2 + P / 2]);
+                            const unsigned long long w2 =
+                                MODE == DDF_B200_MUL ? f2_mul(c2, sf2[t][q2]) : f2_add(c2, sf2[t][q2]);
+                            acc2[q2] = f2_fma(
+                                w2, f2_pack(xr[q2 * S + j * D], xr[(q2 + P / 2) * S + j * D]), acc2[q2]);
                         }
                     } else {
+                        const float c = ldsf(ca);
 #pragma unroll
                         for (int pp = 0; pp < P; ++pp)
                             acc[pp] = fmaf(combine_w<MODE, float>(c, sfr[t][pp]), xr[pp * S + j * D], acc[pp]);
                     }
                 }
             }
-            if (active) store_out<T, P>(outp, acc);
+            float res[P];
+            if constexpr (PK) {
+#pragma unroll
+                for (int q2 = 0; q2 < P / 2; ++q2) f2_unpack(acc2[q2], res[q2], res[q2 + P / 2]);
+            } else {
+#pragma unroll
+                for (int pp = 0; pp < P; ++pp) res[pp] = acc[pp];
+            }
+            if (active) store_out<T, P>(outp, res);
 
             plane_s += (uint32_t)NP * pl.plane_bytes;
-            cfc_s += (uint32_t)NP * (KK * 4);
+            cfc_s += (uint32_t)NP * (KK * 8);
             outp += out_step;
             c_in_b += NP;
             if (c_in_b >= pl.C) {
@@ -566,7 +593,7 @@ bool make_stream_plan(const StreamArgs& a, StreamPlan& pl, uint32_t& smem_bytes,
 
     pl.off_zero = 512;
     pl.off_cfc = pl.off_zero + 256;
-    pl.cfc_stride = round_up((uint32_t)SPL * G::KK * 4u, 16);
+    pl.cfc_stride = round_up((uint32_t)SPL * G::KK * 8u, 16);
     const uint32_t x_region = 32u + (uint32_t)SPL * plane_bytes + 16u + 32u;
     pl.off_rawcf = round_up(x_region, 16);
     pl.stage_stride = round_up(pl.off_rawcf + (uint32_t)SPL * G::KK * G::ES + 32u, 128);
