@@ -249,7 +249,7 @@ def run_ours(args, rank, world, local_rank):
         # per-call durations: each call replayed alone from its own graph over rotating
         # buffer sets larger than L2, timed with CUDA events
         per_shape = []
-        if rank == 0:
+        if rank == 0 and not args.quick:
             for (mode, dtname, C, H, s, x, cf, sf) in cases:
                 nb = algorithmic_bytes(BATCH, C, H, s, 2)
                 nsets = min(24, max(3, (2 * L2_BYTES) // nb + 2))
@@ -317,22 +317,26 @@ def run_ours(args, rank, world, local_rank):
     e2e_value = world * step_bytes / (e2e_ms / e2e_steps * 1e-3) / 1e9
 
     # dominant kernel instance = largest share of the step
-    dom = max(per_shape, key=lambda r: r["us"])
-    roof = {"bound": "hbm", "kernel": f"stream_kernel fwd C={dom['C']} H={dom['H']} s={dom['stride']} "
-                                      f"{dom['dtype']} {dom['combine']}",
-            "achieved": dom["gbs"], "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
-            "frac": round(dom["gbs"] / peak, 4), "frac_of_8000": round(dom["gbs"] / 8000.0, 4),
-            "traffic": None, "us_per_launch": dom["us"], "algorithmic_bytes": dom["bytes"]}
-    tpath = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(tpath):
-        with open(tpath) as f:
-            tj = json.load(f)
-        key = f"{dom['C']}x{dom['H']}s{dom['stride']}"
-        if key in tj:
-            roof["traffic"] = tj[key]
+    roof = None
+    if per_shape:
+        dom = max(per_shape, key=lambda r: r["us"])
+        roof = {"bound": "hbm",
+                "kernel": f"stream_kernel fwd C={dom['C']} H={dom['H']} s={dom['stride']} "
+                          f"{dom['dtype']} {dom['combine']}",
+                "achieved": dom["gbs"], "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+                "frac": round(dom["gbs"] / peak, 4), "frac_of_8000": round(dom["gbs"] / 8000.0, 4),
+                "traffic": None, "us_per_launch": dom["us"], "algorithmic_bytes": dom["bytes"]}
+        # DRAM bytes per launch of that kernel from the committed ncu capture, if any
+        tpath = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(tpath):
+            with open(tpath) as f:
+                tj = json.load(f)
+            key = f"{dom['C']}x{dom['H']}s{dom['stride']}"
+            if key in tj:
+                roof["traffic"] = tj[key]
 
     cpu = None
-    if world == 1 or True:
+    if not args.quick:
         sample_batch = 16
         cpu_sweep_seconds(2)
         secs, nbytes, used = cpu_sweep_seconds(sample_batch)
@@ -358,6 +362,76 @@ def run_ours(args, rank, world, local_rank):
     if args.detail:
         with open(args.detail, "w") as f:
             json.dump(line, f, indent=1)
+
+
+def run_backward(args, rank, world, local_rank):
+    """configs[2]: DDF backward (all three gradients) at B=64, C=256, 28x28, k in
+    {3, 5}, d in {1, 2}, stride 1, mul and add, float32 and bfloat16, through the
+    C ABI with caller-allocated outputs and workspace.  Per case: its own CUDA
+    graph over rotating buffer sets larger than L2, CUDA events."""
+    from ddfnet_b200 import _lib
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    L = _lib.load()
+    peak, peak_kind = peaks()
+    B, C, H = 64, 256, 28
+    rows, total_bytes, total_us = [], 0, 0.0
+    for dtname, dtype, dtc in (("f32", torch.float32, _lib.F32), ("bf16", torch.bfloat16, _lib.BF16)):
+        es = 4 if dtname == "f32" else 2
+        for k in (3, 5):
+            for d in (1, 2):
+                g = torch.Generator().manual_seed(300 + k + d)
+                mk = lambda *shape: torch.randn(*shape, generator=g)
+                base = (mk(B, C, H, H), mk(B, C, H, H).relu_(), mk(B, C, k, k) / 3, mk(B, k * k, H, H) / 3)
+                nb = es * (B * C * H * H + 2 * B * C * H * H + 2 * B * C * k * k + 2 * B * k * k * H * H)
+                nsets = max(3, (2 * L2_BYTES) // nb + 2)
+                sets = []
+                for _ in range(nsets):
+                    go, x, cf, sf = (t.to(dev, dtype) for t in base)
+                    sets.append((go, x, cf, sf, torch.empty_like(x), torch.empty_like(cf), torch.empty_like(sf)))
+                for mode, comb in (("mul", _lib.MUL), ("add", _lib.ADD)):
+                    wsb = int(L.ddf_b200_backward_workspace(B, C, H, H, k, d, 1, comb, dtc, _lib.VARIANT_AUTO))
+                    ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=dev)
+
+                    def call(st):
+                        go, x, cf, sf, gx, gcf, gsf = st
+                        _lib.check(L.ddf_b200_backward(
+                            go.data_ptr(), x.data_ptr(), cf.data_ptr(), sf.data_ptr(), gx.data_ptr(),
+                            gcf.data_ptr(), gsf.data_ptr(), ws.data_ptr(), wsb, B, C, H, H, k, d, 1, comb,
+                            dtc, _lib.VARIANT_AUTO, torch.cuda.current_stream().cuda_stream))
+
+                    for st in sets:
+                        call(st)
+                    torch.cuda.synchronize()
+                    gr = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gr):
+                        for st in sets:
+                            call(st)
+                    for _ in range(3):
+                        gr.replay()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    for _ in range(args.steps):
+                        gr.replay()
+                    b.record()
+                    torch.cuda.synchronize()
+                    us = a.elapsed_time(b) * 1e3 / (args.steps * nsets)
+                    rows.append({"dtype": dtname, "k": k, "d": d, "combine": mode, "us": round(us, 2),
+                                 "bytes": nb, "gbs": round(nb / us / 1e3, 1),
+                                 "frac": round(nb / us / 1e3 / peak, 4),
+                                 "plan": int(L.ddf_b200_plan(B, C, H, H, k, d, 1, comb, dtc, 1))})
+                    total_bytes += nb
+                    total_us += us
+                del sets
+    if rank == 0:
+        print(json.dumps({
+            "metric": "ddf_backward_hbm_gbs", "value": round(total_bytes / total_us / 1e3, 1), "unit": "GB/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": round(total_us / 1e3, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32+bf16 I/O, f32 arithmetic", "data": "synthetic",
+            "config": {"workload": "configs[2]: DDF backward, B=64, C=256, 28x28, k 3/5, d 1/2, mul/add",
+                       "l2": "rotating buffer sets larger than L2"},
+            "peak": peak, "peak_kind": f"of {peak_kind}", "per_case": rows}))
 
 
 def run_model(args, rank, world, local_rank):
@@ -449,14 +523,56 @@ def run_ncu_case(spec):
     print("ok")
 
 
+def run_model_reference(args, rank, world):
+    """CPU baseline of the whole-network workload: the same nn.Module in float32 on
+    the host cores, with the DDF op served by the CPU oracle's unfold composite (a
+    port: the reference has no CPU op).  Reduced batch, stated in the line."""
+    if rank != 0:
+        return
+    import ddfnet_b200.modules as modules
+    from ddfnet_b200.resnet import MODELS
+    from oracle import ddf_oracle
+
+    name = args.model
+    batch = 8
+    orig = modules.ddf
+    modules.ddf = lambda x, cf, sf, k, d, s, comb: ddf_oracle.composite_forward(x, cf, sf, k, d, s, comb)
+    try:
+        torch.manual_seed(0)
+        model = MODELS[name]().eval()
+        x = torch.randn(batch, 3, 224, 224, generator=torch.Generator().manual_seed(1))
+        with torch.no_grad():
+            for _ in range(max(1, min(args.warmup, 1))):
+                model(x)
+            t0 = time.perf_counter()
+            steps = max(1, min(args.steps, 3))
+            for _ in range(steps):
+                model(x)
+            secs = time.perf_counter() - t0
+    finally:
+        modules.ddf = orig
+    val = batch * steps / secs
+    print(json.dumps({
+        "impl": "reference", "metric": f"{name}_images_per_s", "value": round(val, 2), "unit": "images/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": 1, "ms_per_step": round(secs / steps * 1e3, 1),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "float32",
+        "data": "synthetic",
+        "config": {"workload": f"{name} inference on CPU, batch {batch}, 224x224, random init"},
+        "cpu_baseline": {"value": round(val, 2), "unit": "images/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": f"batch {batch}, float32, {os.cpu_count()} logical CPUs"},
+        "e2e": {"value": round(val, 2), "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="op", choices=["op", "model"])
+    ap.add_argument("--workload", default="op", choices=["op", "model", "backward"])
     ap.add_argument("--model", default="ddf_mul_resnet50", choices=sorted(MODEL_CFG))
+    ap.add_argument("--quick", action="store_true",
+                    help="op workload: skip the per-call timings and the CPU baseline (scaling runs)")
     ap.add_argument("--no-graph", action="store_true", help="model workload: eager launches")
     ap.add_argument("--detail", default=None, help="also write the JSON, indented, to this file")
     ap.add_argument("--ncu-case", default=None, metavar="C,H,stride,dtype,combine[,backward]",
@@ -469,7 +585,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        if args.workload == "model":
+            run_model_reference(args, rank, world)
+        else:
+            run_reference(args, rank, world)
         return
     if args.ncu_case:
         run_ncu_case(args.ncu_case)
@@ -483,6 +602,8 @@ def main():
     try:
         if args.workload == "model":
             run_model(args, rank, world, local_rank)
+        elif args.workload == "backward":
+            run_backward(args, rank, world, local_rank)
         else:
             run_ours(args, rank, world, local_rank)
     finally:

@@ -223,7 +223,8 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
                             float v;
                             if constexpr (ES == 4) v = ldsf(src + 4u * e);
                             else v = Word<T>::get(lds16(src + 2u * e), 0);
-                            sts32(dst + 4u * e, __float_as_uint(v));
+                            sts32(dst + 8u * e, __float_as_uint(v));       // (cf, cf) for the
+                            sts32(dst + 8u * e + 4u, __float_as_uint(v));  // two-wide FMA
                         }
                         __syncwarp();
                     }
@@ -302,12 +303,27 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
     const uint32_t go_off = (uint32_t)((oy * pl.OW + ox0) * ES);
     const int my_slot = butterfly_slot<GROUP>(lane);
 
-    float sfr[MUL ? KK : 1][P];
-    float gsf[KK][P];
+    // With P >= 2 the arithmetic is two-wide (mul/fma.f32x2): pixel pp pairs with
+    // pixel pp + P/2 in the spatial-filter registers, the gsf accumulators, the
+    // upstream gradient and the partial sums.
+    // (2-byte element types only: their unpack can target any register, so pairs form
+    // for free; float elements arrive in load order and pairing them costs moves.)
+    constexpr bool PK = P >= 2 && sizeof(T) == 2;
+    constexpr int HP = PK ? P / 2 : 1;
+    float sfr[(MUL && !PK) ? KK : 1][PK ? 1 : P];
+    float gsf[PK ? 1 : KK][PK ? 1 : P];
+    unsigned long long sf2[(MUL && PK) ? KK : 1][HP];
+    unsigned long long gsf2[PK ? KK : 1][HP];
 #pragma unroll
-    for (int t = 0; t < KK; ++t)
+    for (int t = 0; t < KK; ++t) {
+        if constexpr (PK) {
 #pragma unroll
-        for (int pp = 0; pp < P; ++pp) gsf[t][pp] = 0.f;
+            for (int q2 = 0; q2 < HP; ++q2) gsf2[t][q2] = 0ull;
+        } else {
+#pragma unroll
+            for (int pp = 0; pp < P; ++pp) gsf[t][pp] = 0.f;
+        }
+    }
 
     long long b = plane_lo / pl.C;
     int c_in_b = (int)(plane_lo - b * pl.C);
@@ -321,22 +337,36 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
                          (long long)oy * pl.OW + ox0;
 #pragma unroll
             for (int t = 0; t < KK; ++t) {
-                if constexpr (P == 1) {
-                    dst[t * opl] = gsf[t][0];
-                } else if constexpr (P == 2) {
-                    *reinterpret_cast<float2*>(dst + t * opl) = make_float2(gsf[t][0], gsf[t][1]);
+                float v[P];
+                if constexpr (PK) {
+#pragma unroll
+                    for (int q2 = 0; q2 < HP; ++q2) f2_unpack(gsf2[t][q2], v[q2], v[q2 + HP]);
                 } else {
 #pragma unroll
-                    for (int v = 0; v < P / 4; ++v)
-                        reinterpret_cast<float4*>(dst + t * opl)[v] =
-                            make_float4(gsf[t][4 * v], gsf[t][4 * v + 1], gsf[t][4 * v + 2], gsf[t][4 * v + 3]);
+                    for (int pp = 0; pp < P; ++pp) v[pp] = gsf[t][pp];
+                }
+                if constexpr (P == 1) {
+                    dst[t * opl] = v[0];
+                } else if constexpr (P == 2) {
+                    *reinterpret_cast<float2*>(dst + t * opl) = make_float2(v[0], v[1]);
+                } else {
+#pragma unroll
+                    for (int u = 0; u < P / 4; ++u)
+                        reinterpret_cast<float4*>(dst + t * opl)[u] =
+                            make_float4(v[4 * u], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3]);
                 }
             }
         }
 #pragma unroll
-        for (int t = 0; t < KK; ++t)
+        for (int t = 0; t < KK; ++t) {
+            if constexpr (PK) {
 #pragma unroll
-            for (int pp = 0; pp < P; ++pp) gsf[t][pp] = 0.f;
+                for (int q2 = 0; q2 < HP; ++q2) gsf2[t][q2] = 0ull;
+            } else {
+#pragma unroll
+                for (int pp = 0; pp < P; ++pp) gsf[t][pp] = 0.f;
+            }
+        }
     };
 
     int slot = -1;
@@ -355,7 +385,7 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
         const uint32_t goff = (uint32_t)((sfp * pl.gplane_bytes) & 15ull);
         uint32_t xplane_s = STAGE_BASE(slot) + pl.off_x + xoff + (uint32_t)pip * pl.xplane_bytes;
         uint32_t gplane_s = STAGE_BASE(slot) + 32u + goff + (uint32_t)pip * pl.gplane_bytes + go_off;
-        uint32_t cfc_s = sbase + pl.off_cfc + (uint32_t)slot * pl.cfc_stride + (uint32_t)pip * (KK * 4);
+        uint32_t cfc_s = sbase + pl.off_cfc + (uint32_t)slot * pl.cfc_stride + (uint32_t)pip * (KK * 8);
         uint32_t gpart_s = STAGE_BASE(slot) + pl.off_gpart + 4u * (uint32_t)((pip * WPP + wip) * KK);
 
         for (int q = 0; q < npass; ++q) {
@@ -375,9 +405,16 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
                         } else {
                             uint32_t w[G::OUTB / 4];
                             lds_vec<G::OUTB>(a, w);
+                            if constexpr (PK) {
 #pragma unroll
-                            for (int pp = 0; pp < P; ++pp)
-                                sfr[t][pp] = Word<T>::get(w[pp / G::EPW], pp % G::EPW);
+                                for (int q2 = 0; q2 < HP; ++q2)
+                                    sf2[t][q2] = f2_pack(Word<T>::get(w[q2 / G::EPW], q2 % G::EPW),
+                                                         Word<T>::get(w[(q2 + HP) / G::EPW], (q2 + HP) % G::EPW));
+                            } else {
+#pragma unroll
+                                for (int pp = 0; pp < P; ++pp)
+                                    sfr[t][pp] = Word<T>::get(w[pp / G::EPW], pp % G::EPW);
+                            }
                         }
                     }
                     __syncwarp();
@@ -398,11 +435,21 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
                 for (int pp = 0; pp < P; ++pp) g[pp] = Word<T>::get(w[pp / G::EPW], pp % G::EPW);
             }
 
+            unsigned long long g2[HP];
+            if constexpr (PK) {
+#pragma unroll
+                for (int q2 = 0; q2 < HP; ++q2) g2[q2] = f2_pack(g[q2], g[q2 + HP]);
+            }
+
 #pragma unroll
             for (int i0 = 0; i0 < K; i0 += ROWS_PER_GROUP) {
                 float part[GROUP];
+                unsigned long long part2[PK ? GROUP : 1];
 #pragma unroll
-                for (int u = 0; u < GROUP; ++u) part[u] = 0.f;
+                for (int u = 0; u < GROUP; ++u) {
+                    part[u] = 0.f;
+                    if constexpr (PK) part2[u] = 0ull;
+                }
 #pragma unroll
                 for (int ii = 0; ii < ROWS_PER_GROUP; ++ii) {
                     const int i = i0 + ii;
@@ -412,19 +459,45 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
 #pragma unroll
                     for (int j = 0; j < K; ++j) {
                         const int t = i * K + j;
-                        float c = 1.f;
-                        if constexpr (MUL) c = ldsf(cfc_s + 4u * t);
+                        const int u = ii * K + j;
+                        if constexpr (PK) {
+                            unsigned long long c2 = 0ull;
+                            if constexpr (MUL) c2 = lds64_pair(cfc_s + 8u * t);
 #pragma unroll
-                        for (int pp = 0; pp < P; ++pp) {
-                            const float prod = g[pp] * xr[pp * S + j * D];
-                            if constexpr (MUL) {
-                                gsf[t][pp] = fmaf(prod, c, gsf[t][pp]);
-                                part[ii * K + j] = fmaf(prod, sfr[t][pp], part[ii * K + j]);
-                            } else {
-                                gsf[t][pp] += prod;
-                                part[ii * K + j] += prod;
+                            for (int q2 = 0; q2 < HP; ++q2) {
+                                const unsigned long long prod2 =
+                                    f2_mul(g2[q2], f2_pack(xr[q2 * S + j * D], xr[(q2 + HP) * S + j * D]));
+                                if constexpr (MUL) {
+                                    gsf2[t][q2] = f2_fma(prod2, c2, gsf2[t][q2]);
+                                    part2[u] = f2_fma(prod2, sf2[t][q2], part2[u]);
+                                } else {
+                                    gsf2[t][q2] = f2_add(gsf2[t][q2], prod2);
+                                    part2[u] = f2_add(part2[u], prod2);
+                                }
+                            }
+                        } else {
+                            float c = 1.f;
+                            if constexpr (MUL) c = ldsf(cfc_s + 8u * t);
+#pragma unroll
+                            for (int pp = 0; pp < P; ++pp) {
+                                const float prod = g[pp] * xr[pp * S + j * D];
+                                if constexpr (MUL) {
+                                    gsf[t][pp] = fmaf(prod, c, gsf[t][pp]);
+                                    part[u] = fmaf(prod, sfr[t][pp], part[u]);
+                                } else {
+                                    gsf[t][pp] += prod;
+                                    part[u] += prod;
+                                }
                             }
                         }
+                    }
+                }
+                if constexpr (PK) {
+#pragma unroll
+                    for (int u = 0; u < GROUP; ++u) {
+                        float lo, hi;
+                        f2_unpack(part2[u], lo, hi);
+                        part[u] = lo + hi;
                     }
                 }
                 if (!active) {
@@ -437,7 +510,7 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
 
             xplane_s += (uint32_t)NP * pl.xplane_bytes;
             gplane_s += (uint32_t)NP * pl.gplane_bytes;
-            cfc_s += (uint32_t)NP * (KK * 4);
+            cfc_s += (uint32_t)NP * (KK * 8);
             gpart_s += 4u * (uint32_t)(NP * WPP * KK);
             c_in_b += NP;
             if (c_in_b >= pl.C) {
@@ -533,7 +606,10 @@ bool make_bwd_plan(const BwdArgs& a, BwdPlan& pl, uint32_t& smem_bytes, BwdGeome
     if ((planes * G::KK * G::ES) % 16 != 0) return false;
     if (((long long)p.B * sfb) % 16 != 0) return false;
 
-    int PPS = (int)(16384u / ((uint32_t)g.NP * (xpb + gpb)));
+    // Stages of about 48 KB: the service warp's per-stage duties (expanding channel
+    // filters, folding the grad-cf partials, three copies) are a serial chain; with
+    // one pass per stage the compute warps end up waiting for it.
+    int PPS = (int)(49152u / ((uint32_t)g.NP * (xpb + gpb)));
     if (PPS < 1) PPS = 1;
     const long long share = (g.total_passes + a.sm_count - 1) / a.sm_count;
     if (PPS > share) PPS = (int)share;
@@ -543,7 +619,7 @@ bool make_bwd_plan(const BwdArgs& a, BwdPlan& pl, uint32_t& smem_bytes, BwdGeome
 
     pl.off_zero = 512;
     pl.off_cfc = pl.off_zero + 256;
-    pl.cfc_stride = round_up((uint32_t)SPL * G::KK * 4u, 16);
+    pl.cfc_stride = round_up((uint32_t)SPL * G::KK * 8u, 16);
     const uint32_t go_region = 32u + (uint32_t)SPL * gpb + 16u + 32u;
     pl.off_x = round_up(go_region, 16) + 32u;
     const uint32_t x_end = pl.off_x + (uint32_t)SPL * xpb + 16u + 32u;

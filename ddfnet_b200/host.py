@@ -1,7 +1,7 @@
 """``ddf_host``: the DDF forward for callers whose tensors live in host memory.
 
 Inputs are CPU tensors (pinned memory gives full PCIe speed); the result is a
-pinned CPU tensor.  The batch is cut into chunks that are pipelined over two CUDA
+pinned CPU tensor.  The batch is cut into chunks that are pipelined over three CUDA
 streams so that the upload of one chunk, the kernels of another and the download
 of a third overlap (the op is independent per sample, so chunking is exact).
 """
@@ -12,15 +12,30 @@ import torch
 from .op import ddf
 
 
+_STREAMS = {}
+
+
+def _streams(dev, n):
+    key = (dev.index, n)
+    if key not in _STREAMS:
+        _STREAMS[key] = [torch.cuda.Stream(device=dev) for _ in range(n)]
+    return _STREAMS[key]
+
+
 def ddf_host(features, channel_filter, spatial_filter, kernel_size=3, dilation=1, stride=1,
-             kernel_combine='mul', out=None, device=None, chunks=4):
+             kernel_combine='mul', out=None, device=None, chunks=None):
     assert not features.is_cuda and not channel_filter.is_cuda and not spatial_filter.is_cuda
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     b, c, h, w = features.shape
     if out is None:
         out = torch.empty((b, c, h // stride, w // stride), dtype=features.dtype, pin_memory=True)
+    if chunks is None:
+        # about 24 MB of input per chunk: enough chunks to overlap the two copy
+        # directions with the kernels, few enough that host launch cost stays small
+        nbytes = features.numel() * features.element_size()
+        chunks = max(1, min(8, nbytes // (24 << 20)))
     chunks = max(1, min(chunks, b))
-    streams = [torch.cuda.Stream(device=dev) for _ in range(min(2, chunks))]
+    streams = _streams(dev, min(3, chunks))
     cur = torch.cuda.current_stream(dev)
     for st in streams:
         st.wait_stream(cur)
