@@ -180,11 +180,13 @@ static int stream_pixels(const Problem& p, bool bwdx) {
     if (bwdx && s != 1) return 0;
     if (p.W != p.OW * s) return 0;
     const int halo = (k - 1) / 2 * d;
-    static const int cand[4] = {8, 4, 2, 1};
-    for (int ci = 0; ci < 4; ++ci) {
+    // 7 = a whole or half row of a 7- or 14-pixel-wide output (element-wise loads).
+    static const int cand[5] = {8, 4, 7, 2, 1};
+    for (int ci = 0; ci < 5; ++ci) {
         const int P = cand[ci];
         bool built = false;
-        if (k == 3 && d == 1 && s == 1) built = true;
+        if (P == 7) built = k == 3 && d == 1 && (s == 1 || s == 2) && p.OW <= 14;
+        else if (k == 3 && d == 1 && s == 1) built = true;
         else if (k == 3 && d == 1 && s == 2) built = P <= 4;
         else if (k == 3 && d == 2 && s == 1) built = P >= 2;
         else if (k == 5 && d == 1 && s == 1) built = P == 4 || P == 2;

@@ -41,8 +41,8 @@
 namespace ddf {
 
 constexpr int kMaxSlots = 16;          // ring depth upper bound
-constexpr int kMaxComputeThreads = 416;  // 13 warps; + 1 service warp = 448 threads
-// 14 warps = 4 per SM sub-partition at most; each sub-partition has 16K registers,
+constexpr int kMaxComputeThreads = 448;  // 14 warps; + 1 service warp = 480 threads
+// 15 warps = 4 per SM sub-partition at most; each sub-partition has 16K registers,
 // so a thread may use up to 128 (the launch bound below makes ptxas keep to that).
 constexpr int kStreamThreads = kMaxComputeThreads + 32;
 constexpr uint32_t kSmemBudget = 225 * 1024;
@@ -75,8 +75,13 @@ struct Geo {
     static constexpr int EPW = 4 / ES;
     static constexpr int MAINN = P * S;          // elements read as the aligned main vector
     static constexpr int MAINB = MAINN * ES;
-    static constexpr bool SUBWORD = MAINB < 4;   // only P = 1, S = 1 with 2-byte elements
+    // Element-wise path: every input element is fetched with its own shared load.  Used
+    // where a thread's row segment is not a power-of-two vector: P = 1 with 2-byte
+    // elements, and P = 7 (planes 7 or 14 wide: a thread then owns a whole or half row,
+    // which spreads the per-plane overhead over 7 outputs instead of 1 or 2).
+    static constexpr bool SUBWORD = MAINB < 4 || P == 7;
     static constexpr int MAINW = SUBWORD ? 1 : MAINB / 4;
+    static constexpr bool PAIRS = (P >= 2) && (P % 2 == 0);  // pixels pair up for f32x2 math
     static constexpr int NCOL = (P - 1) * S + 2 * HALO + 1;  // input columns a thread touches
     static constexpr int NRE = ((P - 1) * S + HALO + 1 - MAINN) > 0 ? ((P - 1) * S + HALO + 1 - MAINN) : 0;
     static constexpr int NLW = (HALO + EPW - 1) / EPW;   // halo words left of the main vector
@@ -106,16 +111,22 @@ __device__ __forceinline__ void lds_vec(uint32_t a, uint32_t (&w)[NB / 4]) {
 
 // One input row of a thread's window, as floats.  rp = shared address of the
 // first main element (input column ox0*S of that row).
+template <typename T>
+__device__ __forceinline__ uint32_t lds_elem_bits(uint32_t a) {
+    if constexpr (sizeof(T) == 4) return lds32(a);
+    else return lds16(a);
+}
+
 template <typename T, typename G>
 __device__ __forceinline__ void load_row(uint32_t rp, const uint32_t (&lmask)[G::NLM],
                                          const uint32_t (&rmask)[G::NRM], float (&xr)[G::NCOL]) {
     if constexpr (G::SUBWORD) {
 #pragma unroll
         for (int c = 0; c < G::NCOL; ++c) {
-            const int e = c - G::HALO;
-            uint32_t w = lds16(rp + e * G::ES);
+            const int e = c - G::HALO;  // element index relative to the segment's first column
+            uint32_t w = lds_elem_bits<T>(rp + e * G::ES);
             if (e < 0) w &= lmask[0];
-            if (e > 0) w &= rmask[0];
+            if (e >= G::MAINN) w &= rmask[0];
             xr[c] = Word<T>::get(w, 0);
         }
     } else {
@@ -153,7 +164,7 @@ __device__ __forceinline__ void halo_masks(int ox0, int S, int W, uint32_t (&lma
                                            uint32_t (&rmask)[G::NRM]) {
     if constexpr (G::SUBWORD) {
         lmask[0] = ox0 > 0 ? 0xffffffffu : 0u;
-        rmask[0] = ox0 + 1 < W ? 0xffffffffu : 0u;
+        rmask[0] = (ox0 * S + G::MAINN) < W ? 0xffffffffu : 0u;
     } else {
         lmask[0] = 0u;
         rmask[0] = 0u;
@@ -169,7 +180,10 @@ __device__ __forceinline__ void halo_masks(int ox0, int S, int W, uint32_t (&lma
 template <typename T, int P>
 __device__ __forceinline__ void store_out(T* gp, const float (&acc)[P]) {
     constexpr int ES = (int)sizeof(T);
-    if constexpr (ES == 4) {
+    if constexpr (P == 7) {
+#pragma unroll
+        for (int pp = 0; pp < 7; ++pp) Elem<T>::store(gp + pp, acc[pp]);
+    } else if constexpr (ES == 4) {
         if constexpr (P == 1) {
             *reinterpret_cast<float*>(gp) = acc[0];
         } else if constexpr (P == 2) {
@@ -383,7 +397,7 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
 
     // Spatial-filter values of this thread's pixels.  With packed arithmetic they are
     // kept as (pixel q, pixel q + P/2) pairs, the operand layout of mul/fma.f32x2.
-    constexpr bool PK = PACK && P >= 2;
+    constexpr bool PK = PACK && G::PAIRS;
     float sfr[PK ? 1 : KK][PK ? 1 : P];
     unsigned long long sf2[PK ? KK : 1][PK ? P / 2 : 1];
     auto set_sf = [&](int t, int pp, float v) {
@@ -437,8 +451,10 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
 #pragma unroll
                     for (int t = 0; t < KK; ++t) {
                         const uint32_t a = sfs + (uint32_t)(((t * pl.OH + oy) * pl.OW + ox0) * ES);
-                        if constexpr (G::OUTB < 4) {
-                            set_sf(t, 0, Word<T>::get(lds16(a), 0));
+                        if constexpr (G::SUBWORD || G::OUTB < 4) {
+#pragma unroll
+                            for (int pp = 0; pp < P; ++pp)
+                                set_sf(t, pp, Word<T>::get(lds_elem_bits<T>(a + pp * ES), 0));
                         } else {
                             uint32_t w[G::OUTB / 4];
                             lds_vec<G::OUTB>(a, w);
@@ -636,7 +652,7 @@ int stream_launch(const StreamArgs& a, cudaStream_t stream) {
     uint32_t smem = 0;
     int grid = 0;
     if (!make_stream_plan<T, K, D, S, P>(a, pl, smem, grid)) return kNotHandled;
-    constexpr bool PACK = (DDF_PACK_F32X2 != 0) && sizeof(T) == 2 && P >= 2;
+    constexpr bool PACK = (DDF_PACK_F32X2 != 0) && sizeof(T) == 2 && P >= 2 && P % 2 == 0;
     auto kern = stream_kernel<T, K, D, S, P, MODE, BWDX, PACK>;
     // Opt in to the large dynamic shared-memory carve-out once per device and
     // kernel; steady-state launches (and launches under stream capture) then make
