@@ -8,6 +8,8 @@
 #include "generic.cuh"
 #include "stream_fwd.cuh"
 
+#include <cstdlib>
+
 namespace ddf {
 
 __device__ int g_fault_word = 0;
@@ -200,6 +202,27 @@ static int stream_pixels(const Problem& p, bool bwdx) {
     return 0;
 }
 
+// Planes per thread per pass the streaming kernels try first.  DDF_B200_PPT=1 in the
+// environment restores one plane per thread (A/B timing).
+static int stream_ppt() {
+    static const int v = [] {
+        const char* e = std::getenv("DDF_B200_PPT");
+        return (e && e[0] == '1' && e[1] == 0) ? 1 : 2;
+    }();
+    return v;
+}
+
+// Target size of one ring stage: 0 lets the planner choose by plane size;
+// DDF_B200_STAGE_KB=4..96 in the environment fixes it (A/B timing).
+static int stream_stage_bytes() {
+    static const int v = [] {
+        const char* e = std::getenv("DDF_B200_STAGE_KB");
+        const int kb = e ? std::atoi(e) : 0;
+        return (kb >= 4 && kb <= 96 ? kb : 0) * 1024;
+    }();
+    return v;
+}
+
 static int run_stream(const StreamArgs& a, cudaStream_t st) {
     int rc;
     switch (a.p.dtype) {
@@ -212,12 +235,12 @@ static int run_stream(const StreamArgs& a, cudaStream_t st) {
     return rc;
 }
 
-// AUTO prefers the streaming kernels once the problem is big enough to fill the
-// machine; tiny problems launch faster through the generic kernels.
+// AUTO prefers the streaming kernels once there is at least one plane group per SM
+// and a quarter megabyte of input; below that the generic kernels launch faster.
 static bool stream_worthwhile(const Problem& p, int sm_count) {
     const long long planes = (long long)p.B * p.C;
     const long long bytes = planes * p.H * p.W * elem_size(p.dtype);
-    return planes >= sm_count && bytes >= (4ll << 20);
+    return planes >= sm_count && bytes >= (256ll << 10);
 }
 
 }  // namespace ddf
@@ -297,7 +320,7 @@ int ddf_b200_forward(const void* x, const void* cf, const void* sf, void* out, i
         const int P = stream_pixels(p, false);
         const bool want = variant == DDF_B200_VARIANT_STREAM || stream_worthwhile(p, di->sm_count);
         if (P > 0 && want) {
-            StreamArgs a{x, cf, sf, out, p, false, di->sm_count, di->fault, P, di->index};
+            StreamArgs a{x, cf, sf, out, p, false, di->sm_count, di->fault, P, di->index, stream_ppt(), stream_stage_bytes()};
             rc = run_stream(a, st);
             if (rc != kNotHandled) return rc;
         }
@@ -339,7 +362,7 @@ int ddf_b200_backward(const void* go, const void* x, const void* cf, const void*
         if (allow_stream && want) {
             const int P = stream_pixels(p, true);
             if (P > 0) {
-                StreamArgs a{go, cf, sf, gx, p, true, di->sm_count, di->fault, P, di->index};
+                StreamArgs a{go, cf, sf, gx, p, true, di->sm_count, di->fault, P, di->index, stream_ppt(), stream_stage_bytes()};
                 rc = run_stream(a, st);
                 if (rc == 0) done = true;
                 else if (rc != kNotHandled) return rc;

@@ -55,7 +55,8 @@ struct StreamPlan {
     int C, H, W, OH, OW;
     int tasks_per_plane;   // OH*OW / P
     int groups_per_row;    // OW / P
-    int planes_per_pass;   // NP: planes the compute threads cover at once
+    int planes_per_pass;   // NP: planes the compute threads cover at once (= thread_groups * PPT)
+    int thread_groups;     // groups of tasks_per_plane threads; each thread does PPT planes per pass
     int passes_per_stage;  // PPS
     int n_slots;           // ring depth
     int n_compute_warps;
@@ -220,7 +221,11 @@ __device__ __forceinline__ bool warp_test(uint32_t bar, uint32_t parity, int lan
 // BWDX = false: out = DDF forward of `in` (= x).
 // BWDX = true : out = grad-x computed from `in` (= go); stride must be 1.
 // PACK        : accumulate with packed f32x2 FMAs (two pixels per instruction).
-template <typename T, int K, int D, int S, int P, int MODE, bool BWDX, bool PACK>
+// PPT         : planes each thread processes per pass (1 or 2).  With 2 the two planes'
+//               loads and arithmetic are independent and interleave, which hides the
+//               shared-load and dependent-issue latencies that bound the kernel at 14
+//               warps per SM; it needs registers, so it is used where P <= 4.
+template <typename T, int K, int D, int S, int P, int MODE, bool BWDX, bool PACK, int PPT>
 __global__ void __launch_bounds__(kStreamThreads, 1)
 stream_kernel(const __grid_constant__ StreamPlan pl) {
     using G = Geo<T, K, D, S, P>;
@@ -378,7 +383,8 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
     const int TP = pl.tasks_per_plane;
     int pip = tid / TP;  // plane within the pass
     int task = tid - pip * TP;
-    const bool active = pip < NP;
+    const int TG = pl.thread_groups;
+    const bool active = pip < TG;
     if (!active) { pip = 0; task = 0; }
     const int oy = task / pl.groups_per_row;
     const int ox0 = (task - oy * pl.groups_per_row) * P;
@@ -492,51 +498,68 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                 need_sf = false;
             }
 
-            float acc[PK ? 1 : P];
-            unsigned long long acc2[PK ? P / 2 : 1];
-            if constexpr (PK) {
+            float acc[PPT][PK ? 1 : P];
+            unsigned long long acc2[PPT][PK ? P / 2 : 1];
 #pragma unroll
-                for (int q2 = 0; q2 < P / 2; ++q2) acc2[q2] = 0ull;
-            } else {
+            for (int u = 0; u < PPT; ++u) {
+                if constexpr (PK) {
 #pragma unroll
-                for (int pp = 0; pp < P; ++pp) acc[pp] = 0.f;
+                    for (int q2 = 0; q2 < P / 2; ++q2) acc2[u][q2] = 0ull;
+                } else {
+#pragma unroll
+                    for (int pp = 0; pp < P; ++pp) acc[u][pp] = 0.f;
+                }
             }
+            // plane u of this thread within the pass is plane (u * TG + pip) of the pass
+            const uint32_t plane_u = (uint32_t)TG * pl.plane_bytes;
+            const uint32_t cfc_u = (uint32_t)TG * (KK * 8);
 
 #pragma unroll
             for (int i = 0; i < K; ++i) {
-                const uint32_t rp = rowok[i] ? (plane_s + rowoff[i]) : zero_row;
-                float xr[G::NCOL];
-                load_row<T, G>(rp, lmask, rmask, xr);
+                float xr[PPT][G::NCOL];
+#pragma unroll
+                for (int u = 0; u < PPT; ++u) {
+                    const uint32_t rp = rowok[i] ? (plane_s + (uint32_t)u * plane_u + rowoff[i]) : zero_row;
+                    load_row<T, G>(rp, lmask, rmask, xr[u]);
+                }
 #pragma unroll
                 for (int j = 0; j < K; ++j) {
                     const int t = i * K + j;
-                    const uint32_t ca = cfc_s + 8u * (uint32_t)(BWDX ? (KK - 1 - t) : t);
-                    if constexpr (PK) {
-                        const unsigned long long c2 = lds64_pair(ca);
 #pragma unroll
-                        for (int q2 = 0; q2 < P / 2; ++q2) {
-                            const unsigned long long w2 =
-                                MODE == DDF_B200_MUL ? f2_mul(c2, sf2[t][q2]) : f2_add(c2, sf2[t][q2]);
-                            acc2[q2] = f2_fma(
-                                w2, f2_pack(xr[q2 * S + j * D], xr[(q2 + P / 2) * S + j * D]), acc2[q2]);
+                    for (int u = 0; u < PPT; ++u) {
+                        const uint32_t ca = cfc_s + (uint32_t)u * cfc_u + 8u * (uint32_t)(BWDX ? (KK - 1 - t) : t);
+                        if constexpr (PK) {
+                            const unsigned long long c2 = lds64_pair(ca);
+#pragma unroll
+                            for (int q2 = 0; q2 < P / 2; ++q2) {
+                                const unsigned long long w2 =
+                                    MODE == DDF_B200_MUL ? f2_mul(c2, sf2[t][q2]) : f2_add(c2, sf2[t][q2]);
+                                acc2[u][q2] = f2_fma(
+                                    w2, f2_pack(xr[u][q2 * S + j * D], xr[u][(q2 + P / 2) * S + j * D]),
+                                    acc2[u][q2]);
+                            }
+                        } else {
+                            const float c = ldsf(ca);
+#pragma unroll
+                            for (int pp = 0; pp < P; ++pp)
+                                acc[u][pp] = fmaf(combine_w<MODE, float>(c, sfr[t][pp]), xr[u][pp * S + j * D],
+                                                  acc[u][pp]);
                         }
-                    } else {
-                        const float c = ldsf(ca);
-#pragma unroll
-                        for (int pp = 0; pp < P; ++pp)
-                            acc[pp] = fmaf(combine_w<MODE, float>(c, sfr[t][pp]), xr[pp * S + j * D], acc[pp]);
                     }
                 }
             }
-            float res[P];
-            if constexpr (PK) {
 #pragma unroll
-                for (int q2 = 0; q2 < P / 2; ++q2) f2_unpack(acc2[q2], res[q2], res[q2 + P / 2]);
-            } else {
+            for (int u = 0; u < PPT; ++u) {
+                float res[P];
+                if constexpr (PK) {
 #pragma unroll
-                for (int pp = 0; pp < P; ++pp) res[pp] = acc[pp];
+                    for (int q2 = 0; q2 < P / 2; ++q2) f2_unpack(acc2[u][q2], res[q2], res[q2 + P / 2]);
+                } else {
+#pragma unroll
+                    for (int pp = 0; pp < P; ++pp) res[pp] = acc[u][pp];
+                }
+                if (active) store_out<T, P>(outp + (long long)u * TG * out_plane, res);
             }
-            if (active) store_out<T, P>(outp, res);
 
             plane_s += (uint32_t)NP * pl.plane_bytes;
             cfc_s += (uint32_t)NP * (KK * 8);
@@ -569,12 +592,14 @@ struct StreamArgs {
     int* fault;
     int P;       // pixels per thread chosen by the dispatcher
     int device;  // current CUDA device index
+    int ppt;     // planes per thread per pass to try first (2 or 1)
+    int stage_bytes;  // target size of one ring stage; 0 = chosen from the plane size
 };
 
 inline uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
 // Fills the plan; returns false when the problem does not fit this kernel.
-template <typename T, int K, int D, int S, int P>
+template <typename T, int K, int D, int S, int P, int PPT>
 bool make_stream_plan(const StreamArgs& a, StreamPlan& pl, uint32_t& smem_bytes, int& grid) {
     using G = Geo<T, K, D, S, P>;
     const Problem& p = a.p;
@@ -586,9 +611,13 @@ bool make_stream_plan(const StreamArgs& a, StreamPlan& pl, uint32_t& smem_bytes,
     if ((long long)H * W * G::ES > (1ll << 20)) return false;
     const int TP = OH * OW / P;
     if (TP < 1 || TP > kMaxComputeThreads) return false;
-    int NP = kMaxComputeThreads / TP;
-    while (NP > 1 && p.C % NP != 0) --NP;
+    int TG = kMaxComputeThreads / TP;  // thread groups
+    while (TG > 1 && p.C % (TG * PPT) != 0) --TG;
+    if (p.C % (TG * PPT) != 0) return false;
+    const int NP = TG * PPT;  // planes per pass
     const long long planes = (long long)p.B * p.C;
+    // Two planes per thread only while every CTA still gets a fair number of passes.
+    if (PPT > 1 && planes / NP < 8ll * a.sm_count) return false;
     const uint32_t plane_bytes = (uint32_t)(H * W * G::ES);
     const uint32_t sf_bytes = (uint32_t)(G::KK * OH * OW * G::ES);
     // 16-byte rules of the bulk copies.
@@ -598,42 +627,55 @@ bool make_stream_plan(const StreamArgs& a, StreamPlan& pl, uint32_t& smem_bytes,
     if ((planes * G::KK * G::ES) % 16 != 0) return false;
     if (((long long)p.B * sf_bytes) % 16 != 0) return false;
 
-    int PPS = (int)(16384u / ((uint32_t)NP * plane_bytes));
-    if (PPS < 1) PPS = 1;
+    // Stage size.  The service warp does a fixed amount of serial work per stage, so
+    // large planes (>= 4 KB) want stages of two or more passes and about 48 KB;
+    // small planes run best with about 16 KB.  a.stage_bytes > 0 overrides the target.
+    const bool large_plane = plane_bytes >= 4096u;
+    const uint32_t target = a.stage_bytes > 0 ? (uint32_t)a.stage_bytes
+                                              : (large_plane ? 48u << 10 : 16u << 10);
+    int PPS = (int)(target / ((uint32_t)NP * plane_bytes));
+    if (a.stage_bytes <= 0 && large_plane && PPS < 2) PPS = 2;
     const long long total_passes = planes / NP;
     // Do not make stages longer than a CTA's share.
     const long long share = (total_passes + a.sm_count - 1) / a.sm_count;
     if (PPS > share) PPS = (int)share;
     if (PPS < 1) PPS = 1;
-    const int SPL = PPS * NP;
 
     pl.off_zero = 512;
     pl.off_cfc = pl.off_zero + 256;
-    pl.cfc_stride = round_up((uint32_t)SPL * G::KK * 8u, 16);
-    const uint32_t x_region = 32u + (uint32_t)SPL * plane_bytes + 16u + 32u;
-    pl.off_rawcf = round_up(x_region, 16);
-    pl.stage_stride = round_up(pl.off_rawcf + (uint32_t)SPL * G::KK * G::ES + 32u, 128);
     const uint32_t sf_region = round_up(sf_bytes + 32u, 128);
-    int slots = kMaxSlots;
-    for (;; --slots) {
-        if (slots < 2) return false;
-        const uint32_t off_sf = round_up(pl.off_cfc + (uint32_t)slots * pl.cfc_stride, 128);
-        const uint32_t total = off_sf + sf_region + (uint32_t)slots * pl.stage_stride;
-        if (total <= kSmemBudget) {
-            pl.off_sf = off_sf;
-            pl.off_stage0 = off_sf + sf_region;
-            smem_bytes = total;
-            break;
+    // Ring slots that fit with PPS passes per stage (fills the layout fields).
+    auto layout = [&](int pps) {
+        const uint32_t SPL = (uint32_t)pps * NP;
+        pl.cfc_stride = round_up(SPL * G::KK * 8u, 16);
+        const uint32_t x_region = 32u + SPL * plane_bytes + 16u + 32u;
+        pl.off_rawcf = round_up(x_region, 16);
+        pl.stage_stride = round_up(pl.off_rawcf + SPL * G::KK * G::ES + 32u, 128);
+        for (int slots = kMaxSlots; slots >= 1; --slots) {
+            const uint32_t off_sf = round_up(pl.off_cfc + (uint32_t)slots * pl.cfc_stride, 128);
+            const uint32_t total = off_sf + sf_region + (uint32_t)slots * pl.stage_stride;
+            if (total <= kSmemBudget) {
+                pl.off_sf = off_sf;
+                pl.off_stage0 = off_sf + sf_region;
+                smem_bytes = total;
+                return slots;
+            }
         }
-    }
+        return 0;
+    };
+    // Shorten the stages until at least three fit (two when a stage is a single pass).
+    int slots = layout(PPS);
+    while (slots < 3 && PPS > 1) slots = layout(--PPS);
+    if (slots < 2) return false;
     pl.n_slots = slots;
     pl.in = a.in; pl.cf = a.cf; pl.sf = a.sf; pl.out = a.out;
     pl.C = p.C; pl.H = H; pl.W = W; pl.OH = OH; pl.OW = OW;
     pl.tasks_per_plane = TP;
     pl.groups_per_row = OW / P;
     pl.planes_per_pass = NP;
+    pl.thread_groups = TG;
     pl.passes_per_stage = PPS;
-    pl.n_compute_warps = (NP * TP + 31) / 32;
+    pl.n_compute_warps = (TG * TP + 31) / 32;
     pl.total_passes = total_passes;
     pl.plane_bytes = plane_bytes;
     pl.sf_bytes = sf_bytes;
@@ -646,14 +688,14 @@ bool make_stream_plan(const StreamArgs& a, StreamPlan& pl, uint32_t& smem_bytes,
 #define DDF_PACK_F32X2 1
 #endif
 
-template <typename T, int K, int D, int S, int P, int MODE, bool BWDX>
+template <typename T, int K, int D, int S, int P, int MODE, bool BWDX, int PPT = 1>
 int stream_launch(const StreamArgs& a, cudaStream_t stream) {
     StreamPlan pl;
     uint32_t smem = 0;
     int grid = 0;
-    if (!make_stream_plan<T, K, D, S, P>(a, pl, smem, grid)) return kNotHandled;
+    if (!make_stream_plan<T, K, D, S, P, PPT>(a, pl, smem, grid)) return kNotHandled;
     constexpr bool PACK = (DDF_PACK_F32X2 != 0) && sizeof(T) == 2 && P >= 2 && P % 2 == 0;
-    auto kern = stream_kernel<T, K, D, S, P, MODE, BWDX, PACK>;
+    auto kern = stream_kernel<T, K, D, S, P, MODE, BWDX, PACK, PPT>;
     // Opt in to the large dynamic shared-memory carve-out once per device and
     // kernel; steady-state launches (and launches under stream capture) then make
     // no call besides the launch itself.
