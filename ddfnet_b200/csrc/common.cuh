@@ -152,6 +152,9 @@ __device__ __forceinline__ unsigned long long lds64_pair(uint32_t a) {
     asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(a));
     return v;
 }
+__device__ __forceinline__ void sts64(uint32_t a, uint32_t x, uint32_t y) {
+    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(a), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void sts32(uint32_t a, uint32_t v) {
     asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
 }

@@ -343,12 +343,22 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                     const uint32_t coff = (uint32_t)(((unsigned long long)st_first * (KK * ES)) & 15ull);
                     const uint32_t src = STAGE_BASE(slot) + pl.off_rawcf + coff;
                     const uint32_t dst = sbase + pl.off_cfc + (uint32_t)slot * pl.cfc_stride;
-                    for (int e = lane; e < n; e += 32) {
-                        float v;
-                        if constexpr (ES == 4) v = ldsf(src + 4u * e);
-                        else v = Word<T>::get(lds16(src + 2u * e), 0);
-                        sts32(dst + 8u * e, __float_as_uint(v));      // (cf, cf): ready for
-                        sts32(dst + 8u * e + 4u, __float_as_uint(v)); // the two-wide multiply
+                    // Four loads in flight per lane: the loop is latency-bound otherwise and
+                    // the first stage's conversion sits on the kernel's start-up path.
+                    for (int e0 = lane; e0 < n; e0 += 128) {
+                        uint32_t raw[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int e = e0 + 32 * u;
+                            raw[u] = 0u;
+                            if (e < n) raw[u] = ES == 4 ? lds32(src + 4u * e) : lds16(src + 2u * e);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int e = e0 + 32 * u;
+                            const uint32_t v = __float_as_uint(Word<T>::get(raw[u], 0));
+                            if (e < n) sts64(dst + 8u * e, v, v);  // (cf, cf): ready for the two-wide multiply
+                        }
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(BAR_READY(slot));
@@ -403,15 +413,18 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
 
     // Spatial-filter values of this thread's pixels.  With packed arithmetic they are
     // kept as (pixel q, pixel q + P/2) pairs, the operand layout of mul/fma.f32x2.
-    constexpr bool PK = PACK && G::PAIRS;
+    // An odd P pairs up as well: the upper half of the last pair is a dummy pixel whose
+    // result is dropped.
+    constexpr bool PK = PACK && P >= 2;
+    constexpr int PH = (P + 1) / 2;  // pairs per thread
     float sfr[PK ? 1 : KK][PK ? 1 : P];
-    unsigned long long sf2[PK ? KK : 1][PK ? P / 2 : 1];
+    unsigned long long sf2[PK ? KK : 1][PK ? PH : 1];
     auto set_sf = [&](int t, int pp, float v) {
         if constexpr (PK) {
             float lo, hi;
-            f2_unpack(sf2[t][pp % (P / 2)], lo, hi);
-            if (pp < P / 2) lo = v; else hi = v;
-            sf2[t][pp % (P / 2)] = f2_pack(lo, hi);
+            f2_unpack(sf2[t][pp % PH], lo, hi);
+            if (pp < PH) lo = v; else hi = v;
+            sf2[t][pp % PH] = f2_pack(lo, hi);
         } else {
             sfr[t][pp] = v;
         }
@@ -434,10 +447,6 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
     for (int st = 0; st < my_stages; ++st) {
         if (++slot == NST) slot = 0;
         if (slot == 0) ph ^= 1u;
-        if (!mbar_wait(BAR_FULL(slot), ph) || !mbar_wait(BAR_READY(slot), ph)) {
-            atomicCAS(pl.fault, 0, (int)kFaultConsumerFull);
-            return;
-        }
         const int first_pass = st * PPS;
         const int npass = (my_passes - first_pass) < PPS ? (my_passes - first_pass) : PPS;
         const unsigned long long st_first_plane = (unsigned long long)plane_lo + (unsigned long long)first_pass * NP;
@@ -497,14 +506,20 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                 ++seg;
                 need_sf = false;
             }
+            // The stage is awaited after the spatial filter so that, at the start of the
+            // kernel, taking the filter into registers overlaps the stage's arrival.
+            if (q == 0 && (!mbar_wait(BAR_FULL(slot), ph) || !mbar_wait(BAR_READY(slot), ph))) {
+                atomicCAS(pl.fault, 0, (int)kFaultConsumerFull);
+                return;
+            }
 
             float acc[PPT][PK ? 1 : P];
-            unsigned long long acc2[PPT][PK ? P / 2 : 1];
+            unsigned long long acc2[PPT][PK ? PH : 1];
 #pragma unroll
             for (int u = 0; u < PPT; ++u) {
                 if constexpr (PK) {
 #pragma unroll
-                    for (int q2 = 0; q2 < P / 2; ++q2) acc2[u][q2] = 0ull;
+                    for (int q2 = 0; q2 < PH; ++q2) acc2[u][q2] = 0ull;
                 } else {
 #pragma unroll
                     for (int pp = 0; pp < P; ++pp) acc[u][pp] = 0.f;
@@ -531,11 +546,14 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                         if constexpr (PK) {
                             const unsigned long long c2 = lds64_pair(ca);
 #pragma unroll
-                            for (int q2 = 0; q2 < P / 2; ++q2) {
+                            for (int q2 = 0; q2 < PH; ++q2) {
                                 const unsigned long long w2 =
                                     MODE == DDF_B200_MUL ? f2_mul(c2, sf2[t][q2]) : f2_add(c2, sf2[t][q2]);
+                                // the dummy pixel of an odd P re-reads the last column
+                                constexpr int last = G::NCOL - 1;
+                                const int hi_col = (q2 + PH) * S + j * D;
                                 acc2[u][q2] = f2_fma(
-                                    w2, f2_pack(xr[u][q2 * S + j * D], xr[u][(q2 + P / 2) * S + j * D]),
+                                    w2, f2_pack(xr[u][q2 * S + j * D], xr[u][hi_col < last ? hi_col : last]),
                                     acc2[u][q2]);
                             }
                         } else {
@@ -553,7 +571,12 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                 float res[P];
                 if constexpr (PK) {
 #pragma unroll
-                    for (int q2 = 0; q2 < P / 2; ++q2) f2_unpack(acc2[u][q2], res[q2], res[q2 + P / 2]);
+                    for (int q2 = 0; q2 < PH; ++q2) {
+                        float lo, hi;
+                        f2_unpack(acc2[u][q2], lo, hi);
+                        res[q2] = lo;
+                        if (q2 + PH < P) res[q2 + PH] = hi;
+                    }
                 } else {
 #pragma unroll
                     for (int pp = 0; pp < P; ++pp) res[pp] = acc[u][pp];
@@ -687,6 +710,9 @@ bool make_stream_plan(const StreamArgs& a, StreamPlan& pl, uint32_t& smem_bytes,
 #ifndef DDF_PACK_F32X2
 #define DDF_PACK_F32X2 1
 #endif
+#ifndef DDF_PACK_ODD
+#define DDF_PACK_ODD 1
+#endif
 
 template <typename T, int K, int D, int S, int P, int MODE, bool BWDX, int PPT = 1>
 int stream_launch(const StreamArgs& a, cudaStream_t stream) {
@@ -694,7 +720,8 @@ int stream_launch(const StreamArgs& a, cudaStream_t stream) {
     uint32_t smem = 0;
     int grid = 0;
     if (!make_stream_plan<T, K, D, S, P, PPT>(a, pl, smem, grid)) return kNotHandled;
-    constexpr bool PACK = (DDF_PACK_F32X2 != 0) && sizeof(T) == 2 && P >= 2 && P % 2 == 0;
+    constexpr bool PACK = (DDF_PACK_F32X2 != 0) && sizeof(T) == 2 && P >= 2 &&
+                          (P % 2 == 0 || (DDF_PACK_ODD != 0 && PPT == 1));
     auto kern = stream_kernel<T, K, D, S, P, MODE, BWDX, PACK, PPT>;
     // Opt in to the large dynamic shared-memory carve-out once per device and
     // kernel; steady-state launches (and launches under stream capture) then make
