@@ -223,6 +223,16 @@ static int stream_stage_bytes() {
     return v;
 }
 
+// Programmatic dependent launch of the streaming kernels (their start-up overlaps the
+// end of the previous kernel in the stream); DDF_B200_PDL=0 in the environment turns it off.
+static bool stream_overlap_launch() {
+    static const bool v = [] {
+        const char* e = std::getenv("DDF_B200_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return v;
+}
+
 static int run_stream(const StreamArgs& a, cudaStream_t st) {
     int rc;
     switch (a.p.dtype) {
@@ -320,7 +330,7 @@ int ddf_b200_forward(const void* x, const void* cf, const void* sf, void* out, i
         const int P = stream_pixels(p, false);
         const bool want = variant == DDF_B200_VARIANT_STREAM || stream_worthwhile(p, di->sm_count);
         if (P > 0 && want) {
-            StreamArgs a{x, cf, sf, out, p, false, di->sm_count, di->fault, P, di->index, stream_ppt(), stream_stage_bytes()};
+            StreamArgs a{x, cf, sf, out, p, false, di->sm_count, di->fault, P, di->index, stream_ppt(), stream_stage_bytes(), stream_overlap_launch()};
             rc = run_stream(a, st);
             if (rc != kNotHandled) return rc;
         }
@@ -362,7 +372,7 @@ int ddf_b200_backward(const void* go, const void* x, const void* cf, const void*
         if (allow_stream && want) {
             const int P = stream_pixels(p, true);
             if (P > 0) {
-                StreamArgs a{go, cf, sf, gx, p, true, di->sm_count, di->fault, P, di->index, stream_ppt(), stream_stage_bytes()};
+                StreamArgs a{go, cf, sf, gx, p, true, di->sm_count, di->fault, P, di->index, stream_ppt(), stream_stage_bytes(), stream_overlap_launch()};
                 rc = run_stream(a, st);
                 if (rc == 0) done = true;
                 else if (rc != kNotHandled) return rc;

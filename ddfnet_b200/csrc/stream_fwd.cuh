@@ -260,6 +260,12 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
     }
     if (tid < 64) sts32(sbase + pl.off_zero + 4u * tid, 0u);  // 256 zero bytes
     __syncthreads();
+    // Programmatic dependent launch.  When the launch carries the attribute, this grid
+    // may have started while the previous grid in the stream was still finishing: let
+    // the next one do the same, and touch no global memory before the previous grid
+    // has completed and its writes are visible.  Without the attribute both are no-ops.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // This CTA's share of the passes (a pass = NP consecutive planes).
     const long long pass_lo = (pl.total_passes * (long long)blockIdx.x) / gridDim.x;
@@ -617,6 +623,7 @@ struct StreamArgs {
     int device;  // current CUDA device index
     int ppt;     // planes per thread per pass to try first (2 or 1)
     int stage_bytes;  // target size of one ring stage; 0 = chosen from the plane size
+    bool overlap_launch;  // launch with programmatic stream serialization
 };
 
 inline uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
@@ -734,9 +741,17 @@ int stream_launch(const StreamArgs& a, cudaStream_t stream) {
         if (e != cudaSuccess) return (int)e;
         opted_in.fetch_or(bit, std::memory_order_release);
     }
-    const int threads = (pl.n_compute_warps + 1) * 32;
-    kern<<<grid, threads, smem, stream>>>(pl);
-    return (int)cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)((pl.n_compute_warps + 1) * 32));
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = a.overlap_launch ? 1u : 0u;
+    return (int)cudaLaunchKernelEx(&cfg, kern, pl);
 }
 
 // Runtime (k, d, s, P, mode, bwdx) -> instantiation.  Defined once per element
