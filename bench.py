@@ -447,7 +447,13 @@ def run_model(args, rank, world, local_rank):
     dtype, gbatch = MODEL_CFG[name]
     lo, hi = batch_slice(gbatch, rank, world)
     torch.manual_seed(0)
-    model = MODELS[name]().to(dev).to(dtype).eval()
+    model = MODELS[name]().to(dev).eval()
+    if args.fold_bn:
+        from ddfnet_b200.resnet import fold_batchnorm
+        fold_batchnorm(model)
+    model = model.to(dtype)
+    for m in model.ddf_layers():
+        m.fuse_filter_norm = not args.unfused_norm
     g = torch.Generator().manual_seed(1)
     x = torch.randn(gbatch, 3, 224, 224, generator=g)[lo:hi].to(dev, dtype)
     with torch.no_grad():
@@ -496,7 +502,9 @@ def run_model(args, rank, world, local_rank):
             "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": str(dtype).replace("torch.", ""), "data": "synthetic",
             "config": {"workload": f"{name} inference, global batch {gbatch}, 224x224, random init",
-                       "per_gpu_batch": hi - lo, "cuda_graph": graphed},
+                       "per_gpu_batch": hi - lo, "cuda_graph": graphed,
+                       "spatial_filter_norm": "separate torch ops" if args.unfused_norm else "fused into the DDF kernel",
+                       "batchnorm": "folded into the preceding convolutions" if args.fold_bn else "as built"},
             "logits_finite": bool(torch.isfinite(logits).all()), "logits_shape": list(logits.shape)}))
 
 
@@ -574,6 +582,10 @@ def main():
     ap.add_argument("--quick", action="store_true",
                     help="op workload: skip the per-call timings and the CPU baseline (scaling runs)")
     ap.add_argument("--no-graph", action="store_true", help="model workload: eager launches")
+    ap.add_argument("--unfused-norm", action="store_true",
+                    help="model workload: run the spatial FilterNorm as separate torch ops, as the reference does")
+    ap.add_argument("--fold-bn", action="store_true",
+                    help="model workload: fold every BatchNorm that follows a convolution into it")
     ap.add_argument("--detail", default=None, help="also write the JSON, indented, to this file")
     ap.add_argument("--ncu-case", default=None, metavar="C,H,stride,dtype,combine[,backward]",
                     help="profiling aid: run only this case, 6 launches over 3 rotating buffer "

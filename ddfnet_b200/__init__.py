@@ -5,9 +5,9 @@
 arithmetic runs in hand-written sm_100a CUDA kernels behind the C ABI declared
 in include/ddf_b200.h.
 """
-from .op import DDFFunction, ddf
+from .op import DDFFunction, DDFSpatialNormFunction, ddf, ddf_sfnorm
 from .modules import (DDFPack, DDFUpPack, FilterNorm, build_channel_branch,
                       build_spatial_branch)
 
-__all__ = ["ddf", "DDFFunction", "DDFPack", "DDFUpPack", "FilterNorm",
+__all__ = ["ddf", "ddf_sfnorm", "DDFFunction", "DDFSpatialNormFunction", "DDFPack", "DDFUpPack", "FilterNorm",
            "build_spatial_branch", "build_channel_branch"]

@@ -223,16 +223,6 @@ static int stream_stage_bytes() {
     return v;
 }
 
-// Programmatic dependent launch of the streaming kernels (their start-up overlaps the
-// end of the previous kernel in the stream); DDF_B200_PDL=0 in the environment turns it off.
-static bool stream_overlap_launch() {
-    static const bool v = [] {
-        const char* e = std::getenv("DDF_B200_PDL");
-        return !(e && e[0] == '0');
-    }();
-    return v;
-}
-
 static int run_stream(const StreamArgs& a, cudaStream_t st) {
     int rc;
     switch (a.p.dtype) {
@@ -251,6 +241,28 @@ static bool stream_worthwhile(const Problem& p, int sm_count) {
     const long long planes = (long long)p.B * p.C;
     const long long bytes = planes * p.H * p.W * elem_size(p.dtype);
     return planes >= sm_count && bytes >= (256ll << 10);
+}
+
+// Forward for a checked problem: the streaming kernel where it applies, else the generic one.
+static int forward_impl(const Problem& p, const void* x, const void* cf, const void* sf, void* out,
+                        int variant, void* stream) {
+    DeviceInfo* di = nullptr;
+    int rc = device_info(di);
+    if (rc) return rc;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+
+    if (variant != DDF_B200_VARIANT_GENERIC) {
+        const int P = stream_pixels(p, false);
+        const bool want = variant == DDF_B200_VARIANT_STREAM || stream_worthwhile(p, di->sm_count);
+        if (P > 0 && want) {
+            StreamArgs a{x, cf, sf, out, p, false, di->sm_count, di->fault, P, di->index, stream_ppt(),
+                         stream_stage_bytes(), overlap_launch_enabled() && p.k == 3};
+            rc = run_stream(a, st);
+            if (rc != kNotHandled) return rc;
+        }
+        if (variant == DDF_B200_VARIANT_STREAM) return DDF_B200_E_UNSUPPORTED;
+    }
+    return run_generic_forward(p, x, cf, sf, out, di->sm_count, st);
 }
 
 }  // namespace ddf
@@ -321,22 +333,20 @@ int ddf_b200_forward(const void* x, const void* cf, const void* sf, void* out, i
     int rc = check_problem(B, C, H, W, k, d, s, combine, dtype, variant, p);
     if (rc) return rc;
     if (!x || !cf || !sf || !out) return DDF_B200_E_NULL;
-    DeviceInfo* di = nullptr;
-    rc = device_info(di);
-    if (rc) return rc;
-    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    return forward_impl(p, x, cf, sf, out, variant, stream);
+}
 
-    if (variant != DDF_B200_VARIANT_GENERIC) {
-        const int P = stream_pixels(p, false);
-        const bool want = variant == DDF_B200_VARIANT_STREAM || stream_worthwhile(p, di->sm_count);
-        if (P > 0 && want) {
-            StreamArgs a{x, cf, sf, out, p, false, di->sm_count, di->fault, P, di->index, stream_ppt(), stream_stage_bytes(), stream_overlap_launch()};
-            rc = run_stream(a, st);
-            if (rc != kNotHandled) return rc;
-        }
-        if (variant == DDF_B200_VARIANT_STREAM) return DDF_B200_E_UNSUPPORTED;
-    }
-    return run_generic_forward(p, x, cf, sf, out, di->sm_count, st);
+int ddf_b200_forward_sfnorm(const void* x, const void* cf, const void* sf_raw, void* out, int B,
+                            int C, int H, int W, int k, int d, int s, int combine, int dtype,
+                            int variant, double sf_scale, void* stream) {
+    Problem p;
+    int rc = check_problem(B, C, H, W, k, d, s, combine, dtype, variant, p);
+    if (rc) return rc;
+    if (k < 3) return DDF_B200_E_KERNEL;  // the unbiased std over k*k taps needs k*k > 1
+    if (!x || !cf || !sf_raw || !out) return DDF_B200_E_NULL;
+    p.sf_norm = 1;
+    p.sf_scale = sf_scale;
+    return forward_impl(p, x, cf, sf_raw, out, variant, stream);
 }
 
 size_t ddf_b200_backward_workspace(int B, int C, int H, int W, int k, int d, int s, int combine,
@@ -372,7 +382,7 @@ int ddf_b200_backward(const void* go, const void* x, const void* cf, const void*
         if (allow_stream && want) {
             const int P = stream_pixels(p, true);
             if (P > 0) {
-                StreamArgs a{go, cf, sf, gx, p, true, di->sm_count, di->fault, P, di->index, stream_ppt(), stream_stage_bytes(), stream_overlap_launch()};
+                StreamArgs a{go, cf, sf, gx, p, true, di->sm_count, di->fault, P, di->index, stream_ppt(), stream_stage_bytes(), overlap_launch_enabled() && p.k == 3};
                 rc = run_stream(a, st);
                 if (rc == 0) done = true;
                 else if (rc != kNotHandled) return rc;

@@ -44,7 +44,7 @@ int bwd_stream_filters(const Problem& p, const void* go, const void* x, const vo
     BwdGeometry g;
     const int P = bwd_pixels(p, sm_count, g);
     if (P == 0) return kNotHandled;
-    BwdArgs a{go, x, cf, sf, gcf, gsf, workspace, p, sm_count, fault, P, device};
+    BwdArgs a{go, x, cf, sf, gcf, gsf, workspace, p, sm_count, fault, P, device, overlap_launch_enabled() && p.k == 3};
     switch (p.dtype) {
         case DDF_B200_F32: return bwd_dispatch<float>(a, st, launches);
         case DDF_B200_F16: return bwd_dispatch<__half>(a, st, launches);

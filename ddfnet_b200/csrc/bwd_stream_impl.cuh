@@ -139,6 +139,9 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
     }
     if (tid < 64) sts32(sbase + pl.off_zero + 4u * tid, 0u);
     __syncthreads();
+    // Programmatic dependent launch (see stream_kernel): no global access before this.
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const long long pass_lo = (pl.total_passes * (long long)blockIdx.x) / gridDim.x;
     const long long pass_hi = (pl.total_passes * (long long)(blockIdx.x + 1)) / gridDim.x;
@@ -536,16 +539,32 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 gsf_reduce_kernel(const float* __restrict__ scratch, T* __restrict__ gsf, int B, int C, int NP,
                   long long n_per_sample, long long total_passes, int grid_main) {
+    // May have been launched while the filter-gradient kernel was finishing.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     for (long long b = blockIdx.y; b < B; b += gridDim.y) {
         // passes of sample b, and the CTAs of the main kernel that owned them
         const long long q0 = b * C / NP, q1 = (b + 1) * C / NP - 1;
         const long long c0 = ((q0 + 1) * grid_main - 1) / total_passes;
         const long long c1 = ((q1 + 1) * grid_main - 1) / total_passes;
+        // The slots of those CTAs are consecutive: slot j holds n_per_sample floats.
+        const int nslot = (int)(c1 - c0 + 1) * NP;
+        const float* base = scratch + (b + c0) * NP * n_per_sample;
         for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < n_per_sample;
              e += (long long)gridDim.x * blockDim.x) {
-            float tot = 0.f;
-            for (long long c = c0; c <= c1; ++c)
-                for (int u = 0; u < NP; ++u) tot += scratch[((b + c) * NP + u) * n_per_sample + e];
+            // Eight loads in flight per thread; the order of the additions is fixed, so
+            // the result does not depend on scheduling.
+            float acc[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc[u] = 0.f;
+            for (int j0 = 0; j0 < nslot; j0 += 8) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    v[u] = (j0 + u < nslot) ? __ldg(base + (long long)(j0 + u) * n_per_sample + e) : 0.f;
+#pragma unroll
+                for (int u = 0; u < 8; ++u) acc[u] += v[u];
+            }
+            const float tot = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
             Elem<T>::store(gsf + b * n_per_sample + e, tot);
         }
     }
@@ -565,6 +584,7 @@ struct BwdArgs {
     int* fault;
     int P;
     int device;
+    bool overlap_launch;  // launch with programmatic stream serialization
 };
 
 struct BwdGeometry {
@@ -676,18 +696,17 @@ int bwd_launch(const BwdArgs& a, cudaStream_t stream, int* launches) {
         opted_in.fetch_or(bit, std::memory_order_release);
     }
     const int threads = (pl.n_compute_warps + 1) * 32;
-    kern<<<g.grid, threads, smem, stream>>>(pl);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_overlapped(kern, dim3((unsigned)g.grid), dim3((unsigned)threads), smem, stream,
+                                      a.overlap_launch, pl);
     if (e != cudaSuccess) return (int)e;
     ++*launches;
     if (a.gsf) {
         const long long n = (long long)a.p.k * a.p.k * a.p.OH * a.p.OW;
         dim3 grid((unsigned)((n + 255) / 256 < 64 ? (n + 255) / 256 : 64),
                   (unsigned)(a.p.B < 32768 ? a.p.B : 32768));
-        gsf_reduce_kernel<T><<<grid, 256, 0, stream>>>(reinterpret_cast<const float*>(a.workspace),
-                                                       reinterpret_cast<T*>(a.gsf), a.p.B, a.p.C,
-                                                       g.NP, n, g.total_passes, g.grid);
-        e = cudaGetLastError();
+        e = launch_overlapped(gsf_reduce_kernel<T>, grid, dim3(256), 0, stream, a.overlap_launch,
+                              reinterpret_cast<const float*>(a.workspace), reinterpret_cast<T*>(a.gsf),
+                              a.p.B, a.p.C, g.NP, n, g.total_passes, g.grid);
         if (e != cudaSuccess) return (int)e;
         ++*launches;
     }

@@ -19,6 +19,11 @@ struct Problem {
     int k, d, s;
     int combine;       // DDF_B200_MUL / DDF_B200_ADD
     int dtype;         // DDF_B200_F32 ...
+    // Forward only: `sf` holds the raw output of the spatial branch's 1x1 convolution and
+    // the kernel applies the spatial FilterNorm itself (ddf/ddf.py:146-157): per sample and
+    // pixel, over the k*k taps, (v - mean) / (unbiased std + 1e-10) * sf_scale.
+    int sf_norm = 0;
+    double sf_scale = 1.0;
 };
 
 // Status used internally by launchers that may decline a problem.

@@ -44,6 +44,19 @@ generic_forward(const T* __restrict__ x, const T* __restrict__ cf, const T* __re
         const T* xp = x + plane * p.H * p.W;
         const T* cfp = cf + plane * kk;
         const T* sfp = sf + b * kk * opl + (long long)y * p.OW + xo;
+        // Fused spatial FilterNorm: statistics of this pixel's k*k raw filter values.
+        A sf_mean = 0, sf_inv = 1;
+        if (p.sf_norm) {
+            A sum = 0;
+            for (int t = 0; t < kk; ++t) sum += Elem<T>::load(sfp + t * opl);
+            sf_mean = sum / kk;
+            A var = 0;
+            for (int t = 0; t < kk; ++t) {
+                const A dv = Elem<T>::load(sfp + t * opl) - sf_mean;
+                var += dv * dv;
+            }
+            sf_inv = (A)p.sf_scale / (sqrt(var / (kk - 1)) + (A)1e-10);
+        }
         A acc = 0;
         for (int i = 0; i < p.k; ++i) {
             const int iy = y * p.s + (i - r) * p.d;
@@ -52,7 +65,8 @@ generic_forward(const T* __restrict__ x, const T* __restrict__ cf, const T* __re
                 const int ix = xo * p.s + (j - r) * p.d;
                 if (ix < 0 || ix >= p.W) continue;
                 const int t = i * p.k + j;
-                const A w = combine_w<MODE, A>(Elem<T>::load(cfp + t), Elem<T>::load(sfp + t * opl));
+                const A sfv = ((A)Elem<T>::load(sfp + t * opl) - sf_mean) * sf_inv;
+                const A w = combine_w<MODE, A>(Elem<T>::load(cfp + t), sfv);
                 acc += Elem<T>::load(xp + (long long)iy * p.W + ix) * w;
             }
         }

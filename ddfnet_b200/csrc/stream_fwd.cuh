@@ -35,6 +35,7 @@
 #pragma once
 
 #include <atomic>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -65,6 +66,7 @@ struct StreamPlan {
     uint32_t sf_bytes;       // k*k*OH*OW*sizeof(T): one sample's spatial filter
     uint32_t off_zero, off_cfc, cfc_stride, off_sf, off_stage0, stage_stride, off_rawcf;
     int* fault;
+    float sf_scale;  // NORM kernels: output scale of the spatial FilterNorm (gain / k)
 };
 
 template <typename T, int K, int D, int S, int P>
@@ -225,7 +227,9 @@ __device__ __forceinline__ bool warp_test(uint32_t bar, uint32_t parity, int lan
 //               loads and arithmetic are independent and interleave, which hides the
 //               shared-load and dependent-issue latencies that bound the kernel at 14
 //               warps per SM; it needs registers, so it is used where P <= 4.
-template <typename T, int K, int D, int S, int P, int MODE, bool BWDX, bool PACK, int PPT>
+// NORM        : forward only: the values taken from `sf` are raw and the spatial FilterNorm
+//               is applied to them in registers.
+template <typename T, int K, int D, int S, int P, int MODE, bool BWDX, bool PACK, int PPT, bool NORM>
 __global__ void __launch_bounds__(kStreamThreads, 1)
 stream_kernel(const __grid_constant__ StreamPlan pl) {
     using G = Geo<T, K, D, S, P>;
@@ -484,6 +488,53 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                                 set_sf(t, pp, Word<T>::get(w[pp / G::EPW], pp % G::EPW));
                         }
                     }
+                    // Fused spatial FilterNorm (ddf/ddf.py:146-157): each pixel's k*k raw values
+                    // become (v - mean) / (unbiased std + 1e-10) * scale, in registers, once
+                    // per sample.  The dummy pixel of an odd P holds zeros and stays zero.
+                    if constexpr (NORM) {
+                        constexpr float inv_n = 1.f / (float)KK;
+                        constexpr float inv_n1 = 1.f / (float)(KK > 1 ? KK - 1 : 1);
+                        if constexpr (PK) {
+#pragma unroll
+                            for (int q2 = 0; q2 < PH; ++q2) {
+                                unsigned long long sum2 = sf2[0][q2];
+#pragma unroll
+                                for (int t = 1; t < KK; ++t) sum2 = f2_add(sum2, sf2[t][q2]);
+                                const unsigned long long nmean2 =
+                                    f2_mul(sum2, f2_pack(-inv_n, -inv_n));
+                                unsigned long long var2 = 0ull;
+#pragma unroll
+                                for (int t = 0; t < KK; ++t) {
+                                    sf2[t][q2] = f2_add(sf2[t][q2], nmean2);
+                                    var2 = f2_fma(sf2[t][q2], sf2[t][q2], var2);
+                                }
+                                float v0, v1;
+                                f2_unpack(var2, v0, v1);
+                                const unsigned long long inv2 =
+                                    f2_pack(pl.sf_scale / (sqrtf(v0 * inv_n1) + 1e-10f),
+                                            pl.sf_scale / (sqrtf(v1 * inv_n1) + 1e-10f));
+#pragma unroll
+                                for (int t = 0; t < KK; ++t) sf2[t][q2] = f2_mul(sf2[t][q2], inv2);
+                            }
+                        } else {
+#pragma unroll
+                            for (int pp = 0; pp < P; ++pp) {
+                                float sum = 0.f;
+#pragma unroll
+                                for (int t = 0; t < KK; ++t) sum += sfr[t][pp];
+                                const float mean = sum * inv_n;
+                                float var = 0.f;
+#pragma unroll
+                                for (int t = 0; t < KK; ++t) {
+                                    sfr[t][pp] -= mean;
+                                    var = fmaf(sfr[t][pp], sfr[t][pp], var);
+                                }
+                                const float inv = pl.sf_scale / (sqrtf(var * inv_n1) + 1e-10f);
+#pragma unroll
+                                for (int t = 0; t < KK; ++t) sfr[t][pp] *= inv;
+                            }
+                        }
+                    }
                 } else {
                     // grad-x: window tap (i,j) over go pairs with the filter value of
                     // the mirrored tap taken at the neighbouring pixel it came from.
@@ -610,6 +661,35 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
 }
 
 // ------------------------------------------------------------------------ host side
+// Launch with programmatic stream serialization: the grid may start while the previous
+// kernel in the stream is finishing.  Only for kernels that execute griddepcontrol.wait
+// before their first global-memory access.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_overlapped(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, bool overlap, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1u : 0u;
+    return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+// Programmatic dependent launch is on unless DDF_B200_PDL=0 is set in the environment.
+// Callers use it for k = 3 only: the k = 5 'mul' backward measured 3-8 % slower with it.
+inline bool overlap_launch_enabled() {
+    static const bool v = [] {
+        const char* e = std::getenv("DDF_B200_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return v;
+}
+
 struct StreamArgs {
     const void* in;
     const void* cf;
@@ -658,9 +738,9 @@ bool make_stream_plan(const StreamArgs& a, StreamPlan& pl, uint32_t& smem_bytes,
     if (((long long)p.B * sf_bytes) % 16 != 0) return false;
 
     // Stage size.  The service warp does a fixed amount of serial work per stage, so
-    // large planes (>= 4 KB) want stages of two or more passes and about 48 KB;
+    // large planes (>= 3 KB) want stages of two or more passes and about 48 KB;
     // small planes run best with about 16 KB.  a.stage_bytes > 0 overrides the target.
-    const bool large_plane = plane_bytes >= 4096u;
+    const bool large_plane = plane_bytes >= 3072u;
     const uint32_t target = a.stage_bytes > 0 ? (uint32_t)a.stage_bytes
                                               : (large_plane ? 48u << 10 : 16u << 10);
     int PPS = (int)(target / ((uint32_t)NP * plane_bytes));
@@ -710,6 +790,8 @@ bool make_stream_plan(const StreamArgs& a, StreamPlan& pl, uint32_t& smem_bytes,
     pl.plane_bytes = plane_bytes;
     pl.sf_bytes = sf_bytes;
     pl.fault = a.fault;
+    if (a.bwdx && p.sf_norm) return false;  // grad-x takes the normalised filter
+    pl.sf_scale = (float)p.sf_scale;
     grid = (int)(total_passes < a.sm_count ? total_passes : a.sm_count);
     return true;
 }
@@ -721,7 +803,7 @@ bool make_stream_plan(const StreamArgs& a, StreamPlan& pl, uint32_t& smem_bytes,
 #define DDF_PACK_ODD 1
 #endif
 
-template <typename T, int K, int D, int S, int P, int MODE, bool BWDX, int PPT = 1>
+template <typename T, int K, int D, int S, int P, int MODE, bool BWDX, int PPT = 1, bool NORM = false>
 int stream_launch(const StreamArgs& a, cudaStream_t stream) {
     StreamPlan pl;
     uint32_t smem = 0;
@@ -729,7 +811,8 @@ int stream_launch(const StreamArgs& a, cudaStream_t stream) {
     if (!make_stream_plan<T, K, D, S, P, PPT>(a, pl, smem, grid)) return kNotHandled;
     constexpr bool PACK = (DDF_PACK_F32X2 != 0) && sizeof(T) == 2 && P >= 2 &&
                           (P % 2 == 0 || (DDF_PACK_ODD != 0 && PPT == 1));
-    auto kern = stream_kernel<T, K, D, S, P, MODE, BWDX, PACK, PPT>;
+    if (NORM != (a.p.sf_norm != 0)) return kNotHandled;
+    auto kern = stream_kernel<T, K, D, S, P, MODE, BWDX, PACK, PPT, NORM>;
     // Opt in to the large dynamic shared-memory carve-out once per device and
     // kernel; steady-state launches (and launches under stream capture) then make
     // no call besides the launch itself.
@@ -741,17 +824,8 @@ int stream_launch(const StreamArgs& a, cudaStream_t stream) {
         if (e != cudaSuccess) return (int)e;
         opted_in.fetch_or(bit, std::memory_order_release);
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3((unsigned)((pl.n_compute_warps + 1) * 32));
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = a.overlap_launch ? 1u : 0u;
-    return (int)cudaLaunchKernelEx(&cfg, kern, pl);
+    return (int)launch_overlapped(kern, dim3((unsigned)grid), dim3((unsigned)((pl.n_compute_warps + 1) * 32)),
+                                  smem, stream, a.overlap_launch, pl);
 }
 
 // Runtime (k, d, s, P, mode, bwdx) -> instantiation.  Defined once per element

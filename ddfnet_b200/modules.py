@@ -13,7 +13,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch.nn.init import calculate_gain
 
-from .op import ddf
+from .op import ddf, ddf_sfnorm
 
 
 class FilterNorm(nn.Module):
@@ -103,6 +103,10 @@ class DDFPack(nn.Module):
         self.kernel_combine = kernel_combine
         self.spatial_branch = build_spatial_branch(in_channels, kernel_size, head, nonlinearity, stride)
         self.channel_branch = build_channel_branch(in_channels, kernel_size, nonlinearity, se_ratio)
+        # True: the spatial FilterNorm runs inside the DDF kernel (no module, parameter or
+        # state_dict change; the normalised filter is simply never written to memory).
+        # False: the reference's module sequence, op by op.
+        self.fuse_filter_norm = True
 
     def forward(self, x):
         b, c, h, w = x.shape
@@ -110,6 +114,13 @@ class DDFPack(nn.Module):
         k = self.kernel_size
         s = self.stride
         channel_filter = self.channel_branch(x).reshape(b * g, c // g, k, k)
+        if self.fuse_filter_norm and k >= 3:
+            conv, norm = self.spatial_branch[0], self.spatial_branch[1]
+            raw = conv(x).reshape(b * g, -1, h // s, w // s)
+            x = x.reshape(b * g, c // g, h, w)
+            out = ddf_sfnorm(x, channel_filter, raw, self.kernel_size, self.dilation, self.stride,
+                             self.kernel_combine, norm.std)
+            return out.reshape(b, c, h // s, w // s)
         spatial_filter = self.spatial_branch(x).reshape(b * g, -1, h // s, w // s)
         x = x.reshape(b * g, c // g, h, w)
         out = ddf(x, channel_filter, spatial_filter,

@@ -47,34 +47,137 @@ def _require_contiguous(t, name):
         raise RuntimeError(f"{name} must be contiguous ")
 
 
+def _backward_launch(ctx, grad_output, features, channel_filter, spatial_filter, need):
+    """All requested gradients of the op through ddf_b200_backward; tensors are contiguous
+    and of one dtype.  Returns (gx, gcf, gsf), None where not requested."""
+    dt = features.dtype
+    grad_output = grad_output.to(dt).contiguous()
+    b, c, h, w = features.size()
+    k, d, s = ctx.kernel_size, ctx.dilation, ctx.stride
+    need_x, need_cf, need_sf = need
+    dev = features.device
+    gx = torch.empty_like(features) if need_x else None
+    gcf = torch.empty_like(channel_filter) if need_cf else None
+    gsf = torch.empty_like(spatial_filter) if need_sf else None
+
+    lib = _lib.load()
+    comb, dtc = _COMBINE[ctx.op_type], _DTYPES[dt]
+    with torch.cuda.device(dev):
+        ws_bytes = int(lib.ddf_b200_backward_workspace(b, c, h, w, k, d, s, comb, dtc, ctx.bwd_variant))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
+        stream = torch.cuda.current_stream().cuda_stream
+        ptr = lambda t: t.data_ptr() if t is not None else None
+        _lib.check(lib.ddf_b200_backward(
+            grad_output.data_ptr(), features.data_ptr(), channel_filter.data_ptr(),
+            spatial_filter.data_ptr(), ptr(gx), ptr(gcf), ptr(gsf), ptr(ws), ws_bytes,
+            b, c, h, w, k, d, s, comb, dtc, ctx.bwd_variant, stream))
+    return gx, gcf, gsf
+
+
+def _check_shapes(features, channel_filter, spatial_filter, kernel_size, dilation, stride,
+                  kernel_combine, version):
+    """The reference's argument checks (ddf/ddf.py:32-65)."""
+    assert features.is_cuda, 'input feature must be a CUDA tensor.'
+    assert channel_filter.is_cuda, 'channel_filter must be a CUDA tensor.'
+    assert spatial_filter.is_cuda, 'spatial_filter must be a CUDA tensor.'
+    b, c, h, w = features.size()
+    bc, cc, hc, wc = channel_filter.size()
+    assert bc == b and cc == c, \
+        "channel_filter size {} does not match feature size {}".format(
+            channel_filter.size(), features.size())
+    assert hc == kernel_size and wc == kernel_size, \
+        "channel_filter size {} does not match kernel size {}".format(
+            channel_filter.size(), kernel_size)
+    bs, cs, hs, ws = spatial_filter.size()
+    assert bs == b and hs == h // stride and ws == w // stride, \
+        "spatial_filter size {} does not match feature size {} with stride {}".format(
+            spatial_filter.size(), features.size(), stride)
+    assert cs == kernel_size ** 2, \
+        "spatial_filter size {} does not match kernel size {}".format(
+            spatial_filter.size(), kernel_size)
+    assert (kernel_size - 1) % 2 == 0 and kernel_size >= 1 and dilation >= 1 and stride >= 1
+    assert kernel_combine in {'mul', 'add'}, \
+        'only support mul or add combination, instead of {}'.format(kernel_combine)
+    assert version in _VARIANT, "version must be '', 'o' or 'f'"
+    assert channel_filter.device == features.device and spatial_filter.device == features.device
+
+
+def spatial_filter_norm(raw, kernel_size, scale):
+    """FilterNorm(filter_type='spatial') without running statistics (ddf/ddf.py:146-157) on a
+    (B, k*k, H, W) tensor whose heads are already folded into B: each pixel's k*k values are
+    centred, divided by their unbiased std + 1e-10 and multiplied by ``scale``.  Plain torch
+    ops, float32 statistics for 2-byte inputs; used to recompute the filter for the backward
+    of the fused op."""
+    v = raw.float() if raw.dtype in (torch.float16, torch.bfloat16) else raw
+    v = v - v.mean(dim=1, keepdim=True)
+    v = v / (v.std(dim=1, keepdim=True) + 1e-10)
+    return v * scale
+
+
+class DDFSpatialNormFunction(Function):
+    """``ddf`` with the spatial FilterNorm fused into the forward kernel:
+    ``ddf_sfnorm(x, cf, raw, k, d, s, combine, scale, version)`` equals
+    ``ddf(x, cf, FilterNorm_spatial(raw), k, d, s, combine, version)`` with the normalised
+    filter never written to memory (it is kept in float inside the kernel).  The backward
+    recomputes the normalised filter with torch ops, runs the ordinary DDF backward on it
+    and passes the filter gradient back through the normalisation."""
+
+    @staticmethod
+    def forward(ctx, features, channel_filter, spatial_raw, kernel_size=3, dilation=1, stride=1,
+                kernel_combine='mul', scale=1.0, version=''):
+        _check_shapes(features, channel_filter, spatial_raw, kernel_size, dilation, stride,
+                      kernel_combine, version)
+        assert kernel_size >= 3, 'the fused filter norm needs kernel_size >= 3'
+        ctx.in_dtypes = (features.dtype, channel_filter.dtype, spatial_raw.dtype)
+        dt = _common_dtype(features, channel_filter, spatial_raw)
+        features, channel_filter, spatial_raw = (t.to(dt) for t in (features, channel_filter, spatial_raw))
+        _require_contiguous(features, "features")
+        _require_contiguous(channel_filter, "channel_filter")
+        _require_contiguous(spatial_raw, "spatial_filter")
+        ctx.kernel_size, ctx.dilation, ctx.stride = kernel_size, dilation, stride
+        ctx.op_type = kernel_combine
+        ctx.scale = float(scale)
+        ctx.bwd_variant = _lib.VARIANT_GENERIC if version == 'o' else _lib.VARIANT_AUTO
+        b, c, h, w = features.size()
+        output = torch.empty((b, c, h // stride, w // stride), dtype=dt, device=features.device)
+        lib = _lib.load()
+        with torch.cuda.device(features.device):
+            _lib.check(lib.ddf_b200_forward_sfnorm(
+                features.data_ptr(), channel_filter.data_ptr(), spatial_raw.data_ptr(),
+                output.data_ptr(), b, c, h, w, kernel_size, dilation, stride,
+                _COMBINE[kernel_combine], _DTYPES[dt], _VARIANT[version], ctx.scale,
+                torch.cuda.current_stream().cuda_stream))
+        if any(ctx.needs_input_grad[:3]):
+            ctx.save_for_backward(features, channel_filter, spatial_raw)
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        features, channel_filter, spatial_raw = ctx.saved_tensors
+        need_x, need_cf, need_sf = ctx.needs_input_grad[:3]
+        with torch.enable_grad():
+            raw = spatial_raw.detach().requires_grad_(need_sf)
+            normed = spatial_filter_norm(raw, ctx.kernel_size, ctx.scale)
+        gx, gcf, gsf = _backward_launch(ctx, grad_output, features, channel_filter,
+                                        normed.detach().to(features.dtype).contiguous(),
+                                        (need_x, need_cf, need_sf))
+        graw = None
+        if need_sf:
+            (graw,) = torch.autograd.grad(normed, raw, gsf.to(normed.dtype))
+        dx, dcf, dsf = ctx.in_dtypes
+        gx = gx.to(dx) if gx is not None else None
+        gcf = gcf.to(dcf) if gcf is not None else None
+        graw = graw.to(dsf) if graw is not None else None
+        return gx, gcf, graw, None, None, None, None, None, None
+
+
 class DDFFunction(Function):
     @staticmethod
     def forward(ctx, features, channel_filter, spatial_filter,
                 kernel_size=3, dilation=1, stride=1, kernel_combine='mul', version=''):
-        assert features.is_cuda, 'input feature must be a CUDA tensor.'
-        assert channel_filter.is_cuda, 'channel_filter must be a CUDA tensor.'
-        assert spatial_filter.is_cuda, 'spatial_filter must be a CUDA tensor.'
-
+        _check_shapes(features, channel_filter, spatial_filter, kernel_size, dilation, stride,
+                      kernel_combine, version)
         b, c, h, w = features.size()
-        bc, cc, hc, wc = channel_filter.size()
-        assert bc == b and cc == c, \
-            "channel_filter size {} does not match feature size {}".format(
-                channel_filter.size(), features.size())
-        assert hc == kernel_size and wc == kernel_size, \
-            "channel_filter size {} does not match kernel size {}".format(
-                channel_filter.size(), kernel_size)
-        bs, cs, hs, ws = spatial_filter.size()
-        assert bs == b and hs == h // stride and ws == w // stride, \
-            "spatial_filter size {} does not match feature size {} with stride {}".format(
-                spatial_filter.size(), features.size(), stride)
-        assert cs == kernel_size ** 2, \
-            "spatial_filter size {} does not match kernel size {}".format(
-                spatial_filter.size(), kernel_size)
-        assert (kernel_size - 1) % 2 == 0 and kernel_size >= 1 and dilation >= 1 and stride >= 1
-        assert kernel_combine in {'mul', 'add'}, \
-            'only support mul or add combination, instead of {}'.format(kernel_combine)
-        assert version in _VARIANT, "version must be '', 'o' or 'f'"
-        assert channel_filter.device == features.device and spatial_filter.device == features.device
 
         ctx.in_dtypes = (features.dtype, channel_filter.dtype, spatial_filter.dtype)
         dt = _common_dtype(features, channel_filter, spatial_filter)
@@ -110,27 +213,8 @@ class DDFFunction(Function):
     def backward(ctx, grad_output):
         assert grad_output.is_cuda
         features, channel_filter, spatial_filter = ctx.saved_tensors
-        dt = features.dtype
-        grad_output = grad_output.to(dt).contiguous()
-        b, c, h, w = features.size()
-        k, d, s = ctx.kernel_size, ctx.dilation, ctx.stride
-        need_x, need_cf, need_sf = ctx.needs_input_grad[:3]
-        dev = features.device
-        gx = torch.empty_like(features) if need_x else None
-        gcf = torch.empty_like(channel_filter) if need_cf else None
-        gsf = torch.empty_like(spatial_filter) if need_sf else None
-
-        lib = _lib.load()
-        comb, dtc = _COMBINE[ctx.op_type], _DTYPES[dt]
-        with torch.cuda.device(dev):
-            ws_bytes = int(lib.ddf_b200_backward_workspace(b, c, h, w, k, d, s, comb, dtc, ctx.bwd_variant))
-            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
-            stream = torch.cuda.current_stream().cuda_stream
-            ptr = lambda t: t.data_ptr() if t is not None else None
-            _lib.check(lib.ddf_b200_backward(
-                grad_output.data_ptr(), features.data_ptr(), channel_filter.data_ptr(),
-                spatial_filter.data_ptr(), ptr(gx), ptr(gcf), ptr(gsf), ptr(ws), ws_bytes,
-                b, c, h, w, k, d, s, comb, dtc, ctx.bwd_variant, stream))
+        gx, gcf, gsf = _backward_launch(ctx, grad_output, features, channel_filter, spatial_filter,
+                                        ctx.needs_input_grad[:3])
         dx, dcf, dsf = ctx.in_dtypes
         if gx is not None and gx.dtype != dx:
             gx = gx.to(dx)
@@ -142,3 +226,4 @@ class DDFFunction(Function):
 
 
 ddf = DDFFunction.apply
+ddf_sfnorm = DDFSpatialNormFunction.apply

@@ -97,6 +97,34 @@ class DDFResNet(nn.Module):
         return [m for m in self.modules() if isinstance(m, DDFPack)]
 
 
+def _fold(conv: nn.Conv2d, bn: nn.BatchNorm2d) -> nn.Conv2d:
+    """conv followed by an eval-mode BatchNorm as one convolution with a bias."""
+    scale = bn.weight / torch.sqrt(bn.running_var + bn.eps)
+    out = nn.Conv2d(conv.in_channels, conv.out_channels, conv.kernel_size, conv.stride, conv.padding,
+                    conv.dilation, conv.groups, bias=True).to(conv.weight.device, conv.weight.dtype)
+    with torch.no_grad():
+        out.weight.copy_(conv.weight * scale.reshape(-1, 1, 1, 1).to(conv.weight.dtype))
+        bias = conv.bias if conv.bias is not None else torch.zeros_like(bn.running_mean)
+        out.bias.copy_(((bias - bn.running_mean) * scale + bn.bias).to(conv.weight.dtype))
+    return out
+
+
+def fold_batchnorm(model: "DDFResNet") -> "DDFResNet":
+    """Inference-only rewrite, in place: every BatchNorm that directly follows a convolution
+    (stem, conv1 / conv3 of each block, projection shortcuts) is folded into that
+    convolution's weights and bias.  The BatchNorm after each DDFPack stays: the DDF output
+    is not linear in any stored weight.  The model must be in eval mode."""
+    assert not model.training, "fold_batchnorm is for eval-mode models"
+    model.conv1, model.bn1 = _fold(model.conv1, model.bn1), nn.Identity()
+    for m in model.modules():
+        if isinstance(m, DDFBottleneck):
+            m.conv1, m.bn1 = _fold(m.conv1, m.bn1), nn.Identity()
+            m.conv3, m.bn3 = _fold(m.conv3, m.bn3), nn.Identity()
+            if m.downsample is not None:
+                m.downsample = nn.Sequential(_fold(m.downsample[0], m.downsample[1]))
+    return model
+
+
 _LAYERS = {50: [3, 4, 6, 3], 101: [3, 4, 23, 3], 152: [3, 8, 36, 3]}
 
 

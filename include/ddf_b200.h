@@ -84,6 +84,23 @@ int ddf_b200_forward(const void* x, const void* cf, const void* sf, void* out,
                      int B, int C, int H, int W, int k, int d, int s,
                      int combine, int dtype, int variant, void* stream);
 
+/*
+ * Forward with the spatial FilterNorm fused in.  `sf_raw` is the raw output of
+ * the spatial branch's 1x1 convolution, shape (B,k*k,H/s,W/s); the kernel
+ * normalises each pixel's k*k values itself -- (v - mean) / (std + 1e-10) * sf_scale,
+ * std unbiased (divisor k*k - 1), statistics in float -- and then proceeds as
+ * ddf_b200_forward.  Replaces FilterNorm(filter_type='spatial').forward
+ * (ddf/ddf.py:146-157, built by build_spatial_branch, ddf/ddf.py:176-180, which
+ * uses neither a running std nor a running mean) followed by the forward above;
+ * sf_scale is that module's `std` attribute, calculate_gain(nonlinearity) / k
+ * (ddf/ddf.py:135).  With head > 1 the caller has already folded heads into B.
+ * Requires k >= 3.  The backward takes the normalised filter: recompute it and
+ * call ddf_b200_backward.
+ */
+int ddf_b200_forward_sfnorm(const void* x, const void* cf, const void* sf_raw, void* out,
+                            int B, int C, int H, int W, int k, int d, int s,
+                            int combine, int dtype, int variant, double sf_scale, void* stream);
+
 /* Which variant (GENERIC or STREAM) AUTO resolves to for this problem; pointers
  * are assumed 16-byte aligned.  `backward` = 0 for the forward, 1 for the backward.
  * Returns a DDF_B200_VARIANT_* value, or a negative status. */

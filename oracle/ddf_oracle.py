@@ -156,3 +156,39 @@ def py_forward_restatement(feat, channel_att, spatial_att, kernel_size, dilation
                             acc += wgt * float(feat[b, c, yy, xx])
                     out[b, c, y, x] = acc
     return out
+
+
+def filter_norm_spatial(raw: torch.Tensor, head: int, k: int, scale: float) -> torch.Tensor:
+    """FilterNorm(filter_type='spatial') with neither running std nor running mean, restated
+    from ddf/ddf.py:146-152 with explicit loops over the taps (float64): for every sample,
+    head and pixel, the k*k values are centred, divided by (unbiased std + 1e-10) and
+    multiplied by ``scale`` (= calculate_gain(nonlinearity) / k, ddf/ddf.py:135)."""
+    v = raw.double()
+    b, ch, h, w = v.shape
+    kk = k * k
+    assert ch == head * kk
+    v = v.reshape(b, head, kk, h, w)
+    out = torch.empty_like(v)
+    mean = torch.zeros(b, head, h, w, dtype=torch.float64)
+    for t in range(kk):
+        mean += v[:, :, t]
+    mean /= kk
+    var = torch.zeros_like(mean)
+    for t in range(kk):
+        var += (v[:, :, t] - mean) ** 2
+    std = (var / (kk - 1)).sqrt()
+    for t in range(kk):
+        out[:, :, t] = (v[:, :, t] - mean) / (std + 1e-10) * scale
+    return out.reshape(b, ch, h, w)
+
+
+def filter_norm_channel(raw: torch.Tensor, c: int, k: int, std_param: torch.Tensor) -> torch.Tensor:
+    """FilterNorm(filter_type='channel', running_std=True) restated from ddf/ddf.py:158-170:
+    per sample and channel, the k*k values are centred, divided by (unbiased std + 1e-10)
+    and multiplied by the learnable per-(channel, tap) std.  Returns (B, C*k*k), float64."""
+    kk = k * k
+    v = raw.double().reshape(raw.shape[0], c, kk)
+    mean = v.sum(dim=2, keepdim=True) / kk
+    d = v - mean
+    std = ((d * d).sum(dim=2, keepdim=True) / (kk - 1)).sqrt()
+    return (d / (std + 1e-10)).reshape(raw.shape[0], c * kk) * std_param.double()[None, :]

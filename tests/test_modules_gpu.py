@@ -11,12 +11,15 @@ def _with_composite(fn):
     """Runs fn() with ddfnet_b200.modules.ddf replaced by the oracle composite."""
     import ddfnet_b200.modules as modules
     from oracle import ddf_oracle
-    orig = modules.ddf
+    from ddfnet_b200.op import spatial_filter_norm
+    orig, orig_fused = modules.ddf, modules.ddf_sfnorm
     modules.ddf = lambda x, cf, sf, k, d, s, comb: ddf_oracle.composite_forward(x, cf, sf, k, d, s, comb)
+    modules.ddf_sfnorm = lambda x, cf, raw, k, d, s, comb, scale: ddf_oracle.composite_forward(
+        x, cf, spatial_filter_norm(raw, k, scale), k, d, s, comb)
     try:
         return fn()
     finally:
-        modules.ddf = orig
+        modules.ddf, modules.ddf_sfnorm = orig, orig_fused
 
 
 def _run(module, x):
@@ -83,3 +86,25 @@ def test_harness_model_inference(name, dtype):
     # 2-byte inference stays close to the float32 logits
     rel16 = ((got16 - ref).norm() / ref.norm()).item()
     assert rel16 < 0.05, rel16
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(in_channels=64, kernel_size=3, stride=1, head=1, kernel_combine="mul"),
+    dict(in_channels=64, kernel_size=3, stride=2, head=2, kernel_combine="add"),
+])
+def test_ddfpack_fused_filter_norm_equals_module_sequence(cfg):
+    """fuse_filter_norm=True (FilterNorm inside the kernel) against the reference's module
+    sequence on the same weights, forward and all gradients."""
+    from ddfnet_b200 import DDFPack
+    dev = torch.device("cuda:0")
+    torch.manual_seed(3)
+    m = DDFPack(**cfg).to(dev)
+    x = torch.randn(8, cfg["in_channels"], 28, 28, device=dev)
+    assert m.fuse_filter_norm
+    out, gx, grads = _run(m, x)
+    m.fuse_filter_norm = False
+    out_ref, gx_ref, grads_ref = _run(m, x)
+    torch.testing.assert_close(out, out_ref, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(gx, gx_ref, rtol=1e-3, atol=1e-6)
+    for g, gr in zip(grads, grads_ref):
+        torch.testing.assert_close(g, gr, rtol=1e-3, atol=1e-6)

@@ -106,7 +106,8 @@ def test_oracle_gradcheck(shape, d, s, m):
 
 
 def test_oracle_matches_golden_fixtures():
-    files = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.pt")))
+    files = [f for f in sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.pt")))
+             if not os.path.basename(f).startswith("filternorm_")]
     assert files, "no golden fixtures committed"
     for f in files:
         fx = torch.load(f)
@@ -120,3 +121,45 @@ def test_oracle_matches_golden_fixtures():
             if name in fx:
                 scale = max(1.0, fx[name].double().abs().max().item())
                 assert (got - fx[name].double()).abs().max().item() <= tol * scale, (f, name)
+
+
+FN_GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "filternorm_*.pt")))
+
+
+def test_filternorm_fixtures_present():
+    assert len(FN_GOLDEN) >= 5
+
+
+@pytest.mark.parametrize("path", FN_GOLDEN, ids=[os.path.basename(p)[:-3] for p in FN_GOLDEN])
+def test_filter_norm_restatement_matches_reference_module(path):
+    """The oracle's FilterNorm restatements against outputs of the reference's own module
+    (tests/golden/make_golden_filternorm.py), float64."""
+    f = torch.load(path)
+    if f["type"] == "spatial":
+        got = O.filter_norm_spatial(f["raw"], f["head"], f["k"], f["scale"])
+    else:
+        got = O.filter_norm_channel(f["raw"], f["C"], f["k"], f["std"])
+    assert got.shape == f["out"].shape
+    assert (got - f["out"]).abs().max().item() <= 1e-12 * max(1.0, f["out"].abs().max().item())
+
+
+def test_mirror_filter_norm_matches_reference_module():
+    """ddfnet_b200.FilterNorm (the module the package ships) on the same fixtures."""
+    from ddfnet_b200.modules import FilterNorm
+    from ddfnet_b200.op import spatial_filter_norm
+    for path in FN_GOLDEN:
+        f = torch.load(path)
+        if f["type"] == "spatial":
+            m = FilterNorm(f["head"], f["k"], "spatial", f["nonlinearity"])
+            got = m(f["raw"])
+            assert (got - f["out"]).abs().max().item() <= 1e-12
+            # the helper used by the fused op's backward (heads folded into the batch)
+            b, ch, h, w = f["raw"].shape
+            folded = f["raw"].reshape(b * f["head"], -1, h, w)
+            got2 = spatial_filter_norm(folded, f["k"], f["scale"]).reshape(b, ch, h, w)
+            assert (got2 - f["out"]).abs().max().item() <= 1e-12
+        else:
+            m = FilterNorm(f["C"], f["k"], "channel", f["nonlinearity"], running_std=True).double()
+            with torch.no_grad():
+                m.std.copy_(f["std"])
+            assert (m(f["raw"]).detach() - f["out"]).abs().max().item() <= 1e-12
