@@ -434,6 +434,63 @@ def run_backward(args, rank, world, local_rank):
             "peak": peak, "peak_kind": f"of {peak_kind}", "per_case": rows}))
 
 
+def run_sfnorm(args, rank, world, local_rank):
+    """Forward with the spatial FilterNorm fused into the kernel (ddf_sfnorm) against the
+    module sequence it replaces (FilterNorm as torch ops, then ddf), at the sweep's shapes."""
+    from ddfnet_b200 import ddf, ddf_sfnorm
+    from ddfnet_b200.modules import FilterNorm
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    peak, peak_kind = peaks()
+    rows = []
+    scale = 2.0 ** 0.5 / K
+    norm = FilterNorm(1, K, "spatial", "relu")
+    for (C, H, s) in SHAPES:
+        for dtname in ("bf16", "f16"):
+            dtype = {"bf16": torch.bfloat16, "f16": torch.float16}[dtname]
+            nb = algorithmic_bytes(BATCH, C, H, s, 2)
+            nsets = max(3, (2 * L2_BYTES) // nb + 2)
+            sets = [make_case(C, H, s, dtype, BATCH, dev, 500 + i) for i in range(nsets)]
+            times = {}
+            for label, fn in (("fused", lambda x, cf, raw: ddf_sfnorm(x, cf, raw, K, 1, s, "mul", scale)),
+                              ("module_sequence", lambda x, cf, raw: ddf(x, cf, norm(raw), K, 1, s, "mul"))):
+                with torch.no_grad():
+                    for st in sets:
+                        fn(st[0], st[1], st[2])
+                    torch.cuda.synchronize()
+                    gr = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gr):
+                        for st in sets:
+                            fn(st[0], st[1], st[2])
+                    for _ in range(3):
+                        gr.replay()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    for _ in range(args.steps):
+                        gr.replay()
+                    b.record()
+                    torch.cuda.synchronize()
+                    times[label] = a.elapsed_time(b) * 1e3 / (args.steps * nsets)
+            rows.append({"C": C, "H": H, "stride": s, "dtype": dtname, "bytes": nb,
+                         "fused_us": round(times["fused"], 2),
+                         "module_sequence_us": round(times["module_sequence"], 2),
+                         "fused_gbs": round(nb / times["fused"] / 1e3, 1)})
+            del sets
+    tot_b = sum(r["bytes"] for r in rows)
+    tot_f = sum(r["fused_us"] for r in rows)
+    tot_m = sum(r["module_sequence_us"] for r in rows)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "ddf_forward_sfnorm_hbm_gbs", "value": round(tot_b / tot_f / 1e3, 1), "unit": "GB/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": round(tot_f / 1e3, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16+f16 I/O, f32 arithmetic", "data": "synthetic",
+            "config": {"workload": "DDF forward with the spatial FilterNorm fused, sweep shapes, mul, B=128",
+                       "l2": "rotating buffer sets larger than L2"},
+            "module_sequence_ms_per_step": round(tot_m / 1e3, 4),
+            "peak": peak, "peak_kind": f"of {peak_kind}", "per_shape": rows}))
+
+
 def run_model(args, rank, world, local_rank):
     """Whole-network inference throughput (images/s) of the DDF-ResNet harness,
     batch-sharded over the ranks; logits are all-gathered once for checking."""
@@ -450,7 +507,7 @@ def run_model(args, rank, world, local_rank):
     model = MODELS[name]().to(dev).eval()
     if args.fold_bn:
         from ddfnet_b200.resnet import fold_batchnorm
-        fold_batchnorm(model)
+        fold_batchnorm(model, fuse_activations=args.fold_bn == "fused")
     model = model.to(dtype)
     for m in model.ddf_layers():
         m.fuse_filter_norm = not args.unfused_norm
@@ -504,7 +561,8 @@ def run_model(args, rank, world, local_rank):
             "config": {"workload": f"{name} inference, global batch {gbatch}, 224x224, random init",
                        "per_gpu_batch": hi - lo, "cuda_graph": graphed,
                        "spatial_filter_norm": "separate torch ops" if args.unfused_norm else "fused into the DDF kernel",
-                       "batchnorm": "folded into the preceding convolutions" if args.fold_bn else "as built"},
+                       "batchnorm": {None: "as built", "plain": "folded into the preceding convolutions",
+                                     "fused": "folded; conv+bias(+shortcut)+ReLU as single cuDNN calls"}[args.fold_bn]},
             "logits_finite": bool(torch.isfinite(logits).all()), "logits_shape": list(logits.shape)}))
 
 
@@ -577,15 +635,16 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="op", choices=["op", "model", "backward"])
+    ap.add_argument("--workload", default="op", choices=["op", "model", "backward", "sfnorm"])
     ap.add_argument("--model", default="ddf_mul_resnet50", choices=sorted(MODEL_CFG))
     ap.add_argument("--quick", action="store_true",
                     help="op workload: skip the per-call timings and the CPU baseline (scaling runs)")
     ap.add_argument("--no-graph", action="store_true", help="model workload: eager launches")
     ap.add_argument("--unfused-norm", action="store_true",
                     help="model workload: run the spatial FilterNorm as separate torch ops, as the reference does")
-    ap.add_argument("--fold-bn", action="store_true",
-                    help="model workload: fold every BatchNorm that follows a convolution into it")
+    ap.add_argument("--fold-bn", nargs="?", const="plain", default=None, choices=["plain", "fused"],
+                    help="model workload: fold every BatchNorm that follows a convolution into it; "
+                         "'fused' also uses cuDNN's fused conv+bias(+add)+ReLU calls")
     ap.add_argument("--detail", default=None, help="also write the JSON, indented, to this file")
     ap.add_argument("--ncu-case", default=None, metavar="C,H,stride,dtype,combine[,backward]",
                     help="profiling aid: run only this case, 6 launches over 3 rotating buffer "
@@ -616,6 +675,8 @@ def main():
             run_model(args, rank, world, local_rank)
         elif args.workload == "backward":
             run_backward(args, rank, world, local_rank)
+        elif args.workload == "sfnorm":
+            run_sfnorm(args, rank, world, local_rank)
         else:
             run_ours(args, rank, world, local_rank)
     finally:

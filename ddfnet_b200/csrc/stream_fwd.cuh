@@ -214,6 +214,16 @@ __device__ __forceinline__ void store_out(T* gp, const float (&acc)[P]) {
     }
 }
 
+// scale / (sqrt(v) + 1e-10) for v >= 0 without the library's out-of-line slow paths (a call
+// inside the kernel would force spills around it): reciprocal square root refined by one
+// Newton step, then a fast division; a few float ulps in all.
+__device__ __forceinline__ float norm_gain(float v, float scale) {
+    float r = rsqrtf(v);
+    r = r * (1.5f - 0.5f * v * r * r);
+    const float sd = v > 0.f ? v * r : 0.f;
+    return __fdividef(scale, sd + 1e-10f);
+}
+
 __device__ __forceinline__ bool warp_test(uint32_t bar, uint32_t parity, int lane) {
     int ok = 0;
     if (lane == 0) ok = mbar_test(bar, parity) ? 1 : 0;
@@ -511,8 +521,8 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                                 float v0, v1;
                                 f2_unpack(var2, v0, v1);
                                 const unsigned long long inv2 =
-                                    f2_pack(pl.sf_scale / (sqrtf(v0 * inv_n1) + 1e-10f),
-                                            pl.sf_scale / (sqrtf(v1 * inv_n1) + 1e-10f));
+                                    f2_pack(norm_gain(v0 * inv_n1, pl.sf_scale),
+                                            norm_gain(v1 * inv_n1, pl.sf_scale));
 #pragma unroll
                                 for (int t = 0; t < KK; ++t) sf2[t][q2] = f2_mul(sf2[t][q2], inv2);
                             }
@@ -529,7 +539,7 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                                     sfr[t][pp] -= mean;
                                     var = fmaf(sfr[t][pp], sfr[t][pp], var);
                                 }
-                                const float inv = pl.sf_scale / (sqrtf(var * inv_n1) + 1e-10f);
+                                const float inv = norm_gain(var * inv_n1, pl.sf_scale);
 #pragma unroll
                                 for (int t = 0; t < KK; ++t) sfr[t][pp] *= inv;
                             }

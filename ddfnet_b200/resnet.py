@@ -37,8 +37,11 @@ class DDFBottleneck(nn.Module):
         self.bn3 = nn.BatchNorm2d(planes * self.expansion)
         self.act3 = nn.ReLU(inplace=True)
         self.downsample = downsample
+        self.fused_inference = False  # set by fold_batchnorm(..., fuse_activations=True)
 
     def forward(self, x):
+        if self.fused_inference:
+            return self._forward_fused(x)
         shortcut = x
         x = self.act1(self.bn1(self.conv1(x)))
         x = self.act2(self.bn2(self.conv2(x)))
@@ -46,6 +49,16 @@ class DDFBottleneck(nn.Module):
         if self.downsample is not None:
             shortcut = self.downsample(shortcut)
         return self.act3(x + shortcut)
+
+    def _forward_fused(self, x):
+        # After fold_batchnorm: conv1 + bias + ReLU and conv3 + bias + shortcut + ReLU each as
+        # one cuDNN call instead of conv, BatchNorm, (add,) ReLU kernels.
+        shortcut = x if self.downsample is None else self.downsample(x)
+        c1, c3 = self.conv1, self.conv3
+        x = torch.cudnn_convolution_relu(x, c1.weight, c1.bias, c1.stride, c1.padding, c1.dilation, 1)
+        x = self.act2(self.bn2(self.conv2(x)))
+        return torch.cudnn_convolution_add_relu(x, c3.weight, shortcut, 1.0, c3.bias, c3.stride,
+                                                c3.padding, c3.dilation, 1)
 
 
 class DDFResNet(nn.Module):
@@ -62,6 +75,7 @@ class DDFResNet(nn.Module):
         self.layer4 = self._make_layer(512, layers[3], 2, kernel_combine, se_ratio)
         self.global_pool = nn.AdaptiveAvgPool2d(1)
         self.fc = nn.Linear(512 * DDFBottleneck.expansion, num_classes)
+        self.fused_inference = False
         self.init_weights()
 
     def _make_layer(self, planes, blocks, stride, kernel_combine, se_ratio):
@@ -88,6 +102,12 @@ class DDFResNet(nn.Module):
                 nn.init.zeros_(m.bias)
 
     def forward(self, x):
+        if self.fused_inference:
+            c = self.conv1
+            x = self.maxpool(torch.cudnn_convolution_relu(x, c.weight, c.bias, c.stride, c.padding,
+                                                          c.dilation, 1))
+            x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
+            return self.fc(torch.flatten(self.global_pool(x), 1))
         x = self.maxpool(self.act1(self.bn1(self.conv1(x))))
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         return self.fc(torch.flatten(self.global_pool(x), 1))
@@ -109,12 +129,19 @@ def _fold(conv: nn.Conv2d, bn: nn.BatchNorm2d) -> nn.Conv2d:
     return out
 
 
-def fold_batchnorm(model: "DDFResNet") -> "DDFResNet":
+def fold_batchnorm(model: "DDFResNet", fuse_activations: bool = False) -> "DDFResNet":
     """Inference-only rewrite, in place: every BatchNorm that directly follows a convolution
     (stem, conv1 / conv3 of each block, projection shortcuts) is folded into that
     convolution's weights and bias.  The BatchNorm after each DDFPack stays: the DDF output
-    is not linear in any stored weight.  The model must be in eval mode."""
+    is not linear in any stored weight.  The model must be in eval mode.
+
+    fuse_activations=True (CUDA only) additionally routes conv + bias + ReLU and
+    conv + bias + shortcut + ReLU through cuDNN's fused convolution calls."""
     assert not model.training, "fold_batchnorm is for eval-mode models"
+    model.fused_inference = fuse_activations
+    for m in model.modules():
+        if isinstance(m, DDFBottleneck):
+            m.fused_inference = fuse_activations
     model.conv1, model.bn1 = _fold(model.conv1, model.bn1), nn.Identity()
     for m in model.modules():
         if isinstance(m, DDFBottleneck):

@@ -108,3 +108,24 @@ def test_ddfpack_fused_filter_norm_equals_module_sequence(cfg):
     torch.testing.assert_close(gx, gx_ref, rtol=1e-3, atol=1e-6)
     for g, gr in zip(grads, grads_ref):
         torch.testing.assert_close(g, gr, rtol=1e-3, atol=1e-6)
+
+
+def test_folded_fused_inference_matches_plain_model():
+    """fold_batchnorm(fuse_activations=True): same logits as the module-by-module network."""
+    from ddfnet_b200.resnet import DDFResNet, fold_batchnorm
+    dev = torch.device("cuda:0")
+    torch.manual_seed(5)
+    m = DDFResNet([1, 1, 1, 1], "mul").to(dev).eval()
+    for mod in m.modules():
+        if isinstance(mod, torch.nn.BatchNorm2d):
+            mod.running_mean.normal_(0, 0.1)
+            mod.running_var.uniform_(0.5, 2)
+            mod.weight.data.normal_(1, 0.2)
+            mod.bias.data.normal_(0, 0.1)
+    x = torch.randn(4, 3, 224, 224, device=dev)
+    with torch.no_grad():
+        y0 = m(x)
+        fold_batchnorm(m, fuse_activations=True)
+        y1 = m(x)
+    rel = ((y0 - y1).norm() / y0.norm()).item()
+    assert rel < 1e-3, rel  # cuDNN may pick TF32-free but differently ordered kernels
