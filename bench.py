@@ -509,10 +509,14 @@ def run_model(args, rank, world, local_rank):
         from ddfnet_b200.resnet import fold_batchnorm
         fold_batchnorm(model, fuse_activations=args.fold_bn == "fused")
     model = model.to(dtype)
+    if args.channels_last:
+        model = model.to(memory_format=torch.channels_last)
     for m in model.ddf_layers():
         m.fuse_filter_norm = not args.unfused_norm
     g = torch.Generator().manual_seed(1)
     x = torch.randn(gbatch, 3, 224, 224, generator=g)[lo:hi].to(dev, dtype)
+    if args.channels_last:
+        x = x.contiguous(memory_format=torch.channels_last)
     with torch.no_grad():
         for _ in range(max(args.warmup, 3)):
             y = model(x)
@@ -561,6 +565,7 @@ def run_model(args, rank, world, local_rank):
             "config": {"workload": f"{name} inference, global batch {gbatch}, 224x224, random init",
                        "per_gpu_batch": hi - lo, "cuda_graph": graphed,
                        "spatial_filter_norm": "separate torch ops" if args.unfused_norm else "fused into the DDF kernel",
+                       "memory_format": "channels_last around the DDF layers" if args.channels_last else "NCHW",
                        "batchnorm": {None: "as built", "plain": "folded into the preceding convolutions",
                                      "fused": "folded; conv+bias(+shortcut)+ReLU as single cuDNN calls"}[args.fold_bn]},
             "logits_finite": bool(torch.isfinite(logits).all()), "logits_shape": list(logits.shape)}))
@@ -642,6 +647,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="model workload: eager launches")
     ap.add_argument("--unfused-norm", action="store_true",
                     help="model workload: run the spatial FilterNorm as separate torch ops, as the reference does")
+    ap.add_argument("--channels-last", action="store_true",
+                    help="model workload: convolutions in channels_last; each DDFPack converts to NCHW and back")
     ap.add_argument("--fold-bn", nargs="?", const="plain", default=None, choices=["plain", "fused"],
                     help="model workload: fold every BatchNorm that follows a convolution into it; "
                          "'fused' also uses cuDNN's fused conv+bias(+add)+ReLU calls")

@@ -541,14 +541,23 @@ gsf_reduce_kernel(const float* __restrict__ scratch, T* __restrict__ gsf, int B,
                   long long n_per_sample, long long total_passes, int grid_main) {
     // May have been launched while the filter-gradient kernel was finishing.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ long long s_c0;
+    __shared__ int s_nslot;
     for (long long b = blockIdx.y; b < B; b += gridDim.y) {
-        // passes of sample b, and the CTAs of the main kernel that owned them
-        const long long q0 = b * C / NP, q1 = (b + 1) * C / NP - 1;
-        const long long c0 = ((q0 + 1) * grid_main - 1) / total_passes;
-        const long long c1 = ((q1 + 1) * grid_main - 1) / total_passes;
+        // passes of sample b, and the CTAs of the main kernel that owned them: 64-bit
+        // divisions, done by one thread per block instead of by every thread
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const long long q0 = b * C / NP, q1 = (b + 1) * C / NP - 1;
+            const long long c0 = ((q0 + 1) * grid_main - 1) / total_passes;
+            const long long c1 = ((q1 + 1) * grid_main - 1) / total_passes;
+            s_c0 = c0;
+            s_nslot = (int)(c1 - c0 + 1) * NP;
+        }
+        __syncthreads();
         // The slots of those CTAs are consecutive: slot j holds n_per_sample floats.
-        const int nslot = (int)(c1 - c0 + 1) * NP;
-        const float* base = scratch + (b + c0) * NP * n_per_sample;
+        const int nslot = s_nslot;
+        const float* base = scratch + (b + s_c0) * NP * n_per_sample;
         for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < n_per_sample;
              e += (long long)gridDim.x * blockDim.x) {
             // Eight loads in flight per thread; the order of the additions is fixed, so

@@ -113,15 +113,17 @@ class DDFPack(nn.Module):
         g = self.head
         k = self.kernel_size
         s = self.stride
-        channel_filter = self.channel_branch(x).reshape(b * g, c // g, k, k)
+        # The op works on contiguous NCHW; a channels_last network converts here.
+        x = x.contiguous()
+        channel_filter = self.channel_branch(x).reshape(b * g, c // g, k, k).contiguous()
         if self.fuse_filter_norm and k >= 3:
             conv, norm = self.spatial_branch[0], self.spatial_branch[1]
-            raw = conv(x).reshape(b * g, -1, h // s, w // s)
+            raw = conv(x).contiguous().reshape(b * g, -1, h // s, w // s)
             x = x.reshape(b * g, c // g, h, w)
             out = ddf_sfnorm(x, channel_filter, raw, self.kernel_size, self.dilation, self.stride,
                              self.kernel_combine, norm.std)
             return out.reshape(b, c, h // s, w // s)
-        spatial_filter = self.spatial_branch(x).reshape(b * g, -1, h // s, w // s)
+        spatial_filter = self.spatial_branch(x).contiguous().reshape(b * g, -1, h // s, w // s)
         x = x.reshape(b * g, c // g, h, w)
         out = ddf(x, channel_filter, spatial_filter,
                   self.kernel_size, self.dilation, self.stride, self.kernel_combine)
