@@ -22,7 +22,7 @@ SYMBOLS = (
     "ddf_b200_version", "ddf_b200_strerror", "ddf_b200_forward", "ddf_b200_plan",
     "ddf_b200_backward_workspace", "ddf_b200_backward", "ddf_b200_take_fault",
     "ddf_b200_launch_count", "ddf_b200_backward_noalloc", "ddf_b200_backward_noalloc_limit",
-    "ddf_b200_forward_sfnorm",
+    "ddf_b200_forward_sfnorm", "ddf_b200_nhwc_to_nchw", "ddf_b200_nchw_to_nhwc",
 )
 
 
@@ -51,6 +51,10 @@ def load() -> ctypes.CDLL:
         L.ddf_b200_forward.argtypes = [vp] * 4 + [i] * 10 + [vp]
         L.ddf_b200_forward_sfnorm.restype = i
         L.ddf_b200_forward_sfnorm.argtypes = [vp] * 4 + [i] * 10 + [ctypes.c_double, vp]
+        L.ddf_b200_nhwc_to_nchw.restype = i
+        L.ddf_b200_nhwc_to_nchw.argtypes = [vp, vp] + [i] * 5 + [vp]
+        L.ddf_b200_nchw_to_nhwc.restype = i
+        L.ddf_b200_nchw_to_nhwc.argtypes = [vp, vp] + [i] * 5 + [vp, vp, i, vp]
         L.ddf_b200_plan.restype = i
         L.ddf_b200_plan.argtypes = [i] * 10
         L.ddf_b200_backward_workspace.restype = sz

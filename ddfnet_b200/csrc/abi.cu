@@ -14,7 +14,7 @@ namespace ddf {
 
 __device__ int g_fault_word = 0;
 
-static std::atomic<unsigned long long> g_launches{0};
+std::atomic<unsigned long long> g_launches{0};  // also counted from layout.cu
 
 struct DeviceInfo {
     int sm_count = 0;

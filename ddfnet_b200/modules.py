@@ -13,6 +13,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch.nn.init import calculate_gain
 
+from .layout import to_nchw
 from .op import ddf, ddf_sfnorm
 
 
@@ -113,17 +114,20 @@ class DDFPack(nn.Module):
         g = self.head
         k = self.kernel_size
         s = self.stride
-        # The op works on contiguous NCHW; a channels_last network converts here.
-        x = x.contiguous()
-        channel_filter = self.channel_branch(x).reshape(b * g, c // g, k, k).contiguous()
+        # The op works on contiguous NCHW.  In a channels_last network the two branches
+        # still consume the tensor as it came (their convolutions want that layout) and
+        # only the op's operands are converted, by the library's transpose kernel.
+        x_in = x
+        x = to_nchw(x)
+        channel_filter = self.channel_branch(x_in).reshape(b * g, c // g, k, k).contiguous()
         if self.fuse_filter_norm and k >= 3:
             conv, norm = self.spatial_branch[0], self.spatial_branch[1]
-            raw = conv(x).contiguous().reshape(b * g, -1, h // s, w // s)
+            raw = to_nchw(conv(x_in)).reshape(b * g, -1, h // s, w // s)
             x = x.reshape(b * g, c // g, h, w)
             out = ddf_sfnorm(x, channel_filter, raw, self.kernel_size, self.dilation, self.stride,
                              self.kernel_combine, norm.std)
             return out.reshape(b, c, h // s, w // s)
-        spatial_filter = self.spatial_branch(x).contiguous().reshape(b * g, -1, h // s, w // s)
+        spatial_filter = to_nchw(self.spatial_branch(x_in)).reshape(b * g, -1, h // s, w // s)
         x = x.reshape(b * g, c // g, h, w)
         out = ddf(x, channel_filter, spatial_filter,
                   self.kernel_size, self.dilation, self.stride, self.kernel_combine)

@@ -16,6 +16,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
+from .layout import to_channels_last
 from .modules import DDFPack
 
 
@@ -38,6 +39,7 @@ class DDFBottleneck(nn.Module):
         self.act3 = nn.ReLU(inplace=True)
         self.downsample = downsample
         self.fused_inference = False  # set by fold_batchnorm(..., fuse_activations=True)
+        self._bn2_affine = None
 
     def forward(self, x):
         if self.fused_inference:
@@ -50,13 +52,28 @@ class DDFBottleneck(nn.Module):
             shortcut = self.downsample(shortcut)
         return self.act3(x + shortcut)
 
+    def _bn2_scale_shift(self, device):
+        # The eval-mode BatchNorm after the DDFPack as a float32 per-channel affine map; kept
+        # outside the module's buffers so that .half() / .to(dtype) leave it in float32.
+        if self._bn2_affine is None or self._bn2_affine[0].device != device:
+            bn = self.bn2
+            scale = bn.weight.detach().float() / torch.sqrt(bn.running_var.float() + bn.eps)
+            shift = bn.bias.detach().float() - bn.running_mean.float() * scale
+            self._bn2_affine = (scale.contiguous(), shift.contiguous())
+        return self._bn2_affine
+
     def _forward_fused(self, x):
         # After fold_batchnorm: conv1 + bias + ReLU and conv3 + bias + shortcut + ReLU each as
         # one cuDNN call instead of conv, BatchNorm, (add,) ReLU kernels.
         shortcut = x if self.downsample is None else self.downsample(x)
         c1, c3 = self.conv1, self.conv3
         x = torch.cudnn_convolution_relu(x, c1.weight, c1.bias, c1.stride, c1.padding, c1.dilation, 1)
-        x = self.act2(self.bn2(self.conv2(x)))
+        x = self.conv2(x)  # DDFPack: contiguous NCHW out
+        if shortcut.is_contiguous(memory_format=torch.channels_last) and not shortcut.is_contiguous():
+            # channels_last network: BatchNorm + ReLU ride on the conversion back to NHWC
+            x = to_channels_last(x, *self._bn2_scale_shift(x.device), relu=True)
+        else:
+            x = self.act2(self.bn2(x))
         return torch.cudnn_convolution_add_relu(x, c3.weight, shortcut, 1.0, c3.bias, c3.stride,
                                                 c3.padding, c3.dilation, 1)
 
@@ -142,6 +159,7 @@ def fold_batchnorm(model: "DDFResNet", fuse_activations: bool = False) -> "DDFRe
     for m in model.modules():
         if isinstance(m, DDFBottleneck):
             m.fused_inference = fuse_activations
+            m._bn2_affine = None  # rebuilt lazily from bn2 on first use
     model.conv1, model.bn1 = _fold(model.conv1, model.bn1), nn.Identity()
     for m in model.modules():
         if isinstance(m, DDFBottleneck):

@@ -170,6 +170,24 @@ int ddf_b200_backward_noalloc(const void* go, const void* x, const void* cf, con
 size_t ddf_b200_backward_noalloc_limit(void);
 
 /*
+ * Layout adapters for a channels-last (NHWC) network around the NCHW op: tiled
+ * transposes of (B,H,W,C) <-> (B,C,H,W).  The reference has no counterpart: its
+ * op rejects non-contiguous input (ddf/src/cuda/ddf_mul_cuda.cpp:28-32), so a
+ * channels_last model (train.py --channels-last) pays generic strided copies
+ * around every DDF layer.
+ *
+ * ddf_b200_nchw_to_nhwc can apply, on the way, dst = src * ch_scale[c] + ch_shift[c]
+ * (both float arrays of C values, both NULL for none) and then max(., 0) when
+ * `relu` is non-zero -- an eval-mode BatchNorm and ReLU following the op.
+ * dtype: F32, F16 or BF16.  src and dst must not overlap and must be 16-byte
+ * aligned (DDF_B200_E_UNSUPPORTED otherwise).
+ */
+int ddf_b200_nhwc_to_nchw(const void* src, void* dst, int B, int C, int H, int W, int dtype,
+                          void* stream);
+int ddf_b200_nchw_to_nhwc(const void* src, void* dst, int B, int C, int H, int W, int dtype,
+                          const float* ch_scale, const float* ch_shift, int relu, void* stream);
+
+/*
  * Reads and clears the per-device fault word that the streaming kernels set
  * when one of their bounded waits runs out (they then stop instead of spinning).
  * Synchronises the device.  0 = no fault recorded; otherwise a positive code
