@@ -23,6 +23,7 @@ SYMBOLS = (
     "ddf_b200_backward_workspace", "ddf_b200_backward", "ddf_b200_take_fault",
     "ddf_b200_launch_count", "ddf_b200_backward_noalloc", "ddf_b200_backward_noalloc_limit",
     "ddf_b200_forward_sfnorm", "ddf_b200_nhwc_to_nchw", "ddf_b200_nchw_to_nhwc",
+    "ddf_b200_channel_filter", "ddf_b200_channel_filter_slice",
 )
 
 
@@ -55,6 +56,10 @@ def load() -> ctypes.CDLL:
         L.ddf_b200_nhwc_to_nchw.argtypes = [vp, vp] + [i] * 5 + [vp]
         L.ddf_b200_nchw_to_nhwc.restype = i
         L.ddf_b200_nchw_to_nhwc.argtypes = [vp, vp] + [i] * 5 + [vp, vp, i, vp]
+        L.ddf_b200_channel_filter_slice.restype = i
+        L.ddf_b200_channel_filter_slice.argtypes = [i]
+        L.ddf_b200_channel_filter.restype = i
+        L.ddf_b200_channel_filter.argtypes = [vp, i, ctypes.c_float] + [vp] * 6 + [i] * 5 + [vp]
         L.ddf_b200_plan.restype = i
         L.ddf_b200_plan.argtypes = [i] * 10
         L.ddf_b200_backward_workspace.restype = sz

@@ -90,6 +90,49 @@ def build_channel_branch(in_channels, kernel_size, nonlinearity='relu', se_ratio
         FilterNorm(in_channels, kernel_size, 'channel', nonlinearity, running_std=True))
 
 
+def channel_filter_fused(branch: nn.Sequential, x: torch.Tensor, kernel_size: int):
+    """The channel branch (``build_channel_branch``) through the library's single kernel:
+    a float32 global average pool (one torch reduction) followed by
+    ``ddf_b200_channel_filter``.  Returns (B, C, k, k) in x's dtype, or None when the case
+    is outside the kernel's range or gradients are being recorded (the caller then runs the
+    module sequence)."""
+    from . import _lib
+    from .op import _DTYPES
+    conv1, conv2, norm = branch[1], branch[3], branch[4]
+    b, c = x.shape[0], x.shape[1]
+    mid = conv1.out_channels
+    params = (conv1.weight, conv1.bias, conv2.weight, conv2.bias, norm.std)
+    if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in params)):
+        return None
+    if (not x.is_cuda or x.dtype not in _DTYPES or x.dtype == torch.float64 or kernel_size not in (3, 5)
+            or c > 2048 or mid > 512 or not norm.runing_std or norm.runing_mean
+            or any(p is None or p.dtype != x.dtype for p in params)):
+        return None
+    pooled = x.mean(dim=(2, 3), dtype=torch.float32).contiguous()
+    out = torch.empty((b, c, kernel_size, kernel_size), dtype=x.dtype, device=x.device)
+    # 1x1 weights: (out, in, 1, 1) is the same memory in contiguous and channels_last form
+    w1 = conv1.weight.detach().reshape(mid, c).contiguous()
+    # second weight re-laid-out as (C/CW, mid, k*k, CW): one contiguous run per CTA; cached
+    # until the parameter changes
+    lib = _lib.load()
+    cw = int(lib.ddf_b200_channel_filter_slice(c))
+    if c % 8 != 0 or c % cw != 0:
+        return None
+    key = (conv2.weight.data_ptr(), conv2.weight._version, conv2.weight.dtype)
+    cache = getattr(branch, "_ddf_w2s", None)
+    if cache is None or cache[0] != key:
+        w2s = conv2.weight.detach().reshape(c // cw, cw, kernel_size ** 2, mid).permute(0, 3, 2, 1).contiguous()
+        cache = (key, w2s)
+        branch._ddf_w2s = cache
+    w2 = cache[1]
+    with torch.cuda.device(x.device):
+        _lib.check(lib.ddf_b200_channel_filter(
+            pooled.data_ptr(), 1, 1.0, w1.data_ptr(), conv1.bias.data_ptr(), w2.data_ptr(),
+            conv2.bias.data_ptr(), norm.std.data_ptr(), out.data_ptr(), b, c, mid, kernel_size,
+            _DTYPES[x.dtype], torch.cuda.current_stream().cuda_stream))
+    return out
+
+
 class DDFPack(nn.Module):
     """Drop-in for a k x k convolution built on the DDF op, ddf/ddf.py:195-222."""
 
@@ -108,6 +151,9 @@ class DDFPack(nn.Module):
         # state_dict change; the normalised filter is simply never written to memory).
         # False: the reference's module sequence, op by op.
         self.fuse_filter_norm = True
+        # True: when no gradients are recorded, the channel branch after its average pool
+        # (two 1x1 convolutions, ReLU, FilterNorm) runs as one library kernel.
+        self.fuse_channel_branch = True
 
     def forward(self, x):
         b, c, h, w = x.shape
@@ -119,7 +165,10 @@ class DDFPack(nn.Module):
         # only the op's operands are converted, by the library's transpose kernel.
         x_in = x
         x = to_nchw(x)
-        channel_filter = self.channel_branch(x_in).reshape(b * g, c // g, k, k).contiguous()
+        channel_filter = channel_filter_fused(self.channel_branch, x_in, k) if self.fuse_channel_branch else None
+        if channel_filter is None:
+            channel_filter = self.channel_branch(x_in)
+        channel_filter = channel_filter.reshape(b * g, c // g, k, k).contiguous()
         if self.fuse_filter_norm and k >= 3:
             conv, norm = self.spatial_branch[0], self.spatial_branch[1]
             raw = to_nchw(conv(x_in)).reshape(b * g, -1, h // s, w // s)

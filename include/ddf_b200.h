@@ -188,6 +188,35 @@ int ddf_b200_nchw_to_nhwc(const void* src, void* dst, int B, int C, int H, int W
                           const float* ch_scale, const float* ch_shift, int relu, void* stream);
 
 /*
+ * The channel branch of a DDF layer after its global average pool, as one launch:
+ * 1x1 convolution C -> mid (w1 (mid,C), b1), ReLU, 1x1 convolution mid -> C*k*k
+ * (w2s, b2), then FilterNorm(filter_type='channel', running_std=True):
+ * per sample and channel the k*k values are centred, divided by their unbiased
+ * std + 1e-10 and multiplied by gain[c*k*k + t] (the module's learnable `std`).
+ * Replaces build_channel_branch minus its AdaptiveAvgPool2d (ddf/ddf.py:183-192,
+ * FilterNorm at ddf/ddf.py:158-170), which the reference runs as about ten small
+ * launches.  Weights, biases, gain and the output cf (B,C,k,k) have element type
+ * `dtype` (F32, F16, BF16); arithmetic is float.
+ *
+ * w2s is the second convolution's weight (C*k*k, mid) RE-LAID-OUT as
+ * (C / CW, mid, k*k, CW) with CW = ddf_b200_channel_filter_slice(C) channels per
+ * slice -- w2.reshape(C/CW, CW, k*k, mid).permute(0, 3, 2, 1) -- so that each CTA's
+ * share is one contiguous run for the bulk copies that feed it; do it once and keep
+ * it (inference weights do not change).  w1 and w2s must be 16-byte aligned.
+ *
+ * pooled: float sums of x over pixels, laid out (B, n_partials, C); the kernel
+ * adds the n_partials rows in order and multiplies by pool_scale (pass the mean
+ * itself with n_partials = 1, pool_scale = 1).  k = 3 or 5, C <= 2048 and a multiple
+ * of 8 (of 256 above 256), mid <= 512 (DDF_B200_E_UNSUPPORTED otherwise).  Inference
+ * path: no gradients.
+ */
+int ddf_b200_channel_filter_slice(int C);
+int ddf_b200_channel_filter(const float* pooled, int n_partials, float pool_scale,
+                            const void* w1, const void* b1, const void* w2s, const void* b2,
+                            const void* gain, void* cf, int B, int C, int mid, int k,
+                            int dtype, void* stream);
+
+/*
  * Reads and clears the per-device fault word that the streaming kernels set
  * when one of their bounded waits runs out (they then stop instead of spinning).
  * Synchronises the device.  0 = no fault recorded; otherwise a positive code
