@@ -7,7 +7,8 @@
 // FilterNorm(filter_type='channel', running_std=True) (ddf/ddf.py:158-170).  The reference
 // runs this as about ten small launches per layer; all arithmetic here is float.
 //
-// One CTA serves kSB samples and a slice of CW <= 256 channels.  Both weight matrices reach
+// One CTA (16 warps) serves kSB = 4 samples and a slice of CW <= 256 channels; in the second
+// layer a thread owns one channel and two of the samples.  Both weight matrices reach
 // the CTA through a ring of shared-memory slots filled by untiled TMA bulk copies (one
 // elected thread issues them a few chunks ahead), so the inner loops read shared memory
 // only: with a single CTA of eight warps per SM, loops over global loads were bound by
@@ -30,7 +31,8 @@ extern std::atomic<unsigned long long> g_launches;
 int device_facts(int* sm_count, int** fault, int* index);
 
 constexpr int kSB = 4;               // samples per CTA
-constexpr int kCbThreads = 256;      // 8 warps; also the widest channel slice
+constexpr int kCbSlice = 256;        // widest channel slice of a CTA
+constexpr int kCbThreads = 512;      // 16 warps: two threads per channel, two samples each
 constexpr int kCbSlots = 3;
 constexpr uint32_t kCbChunk = 48 * 1024;  // bytes per ring slot
 constexpr int kCbMaxC = 2048;
@@ -129,17 +131,23 @@ channel_branch_kernel(const __grid_constant__ CbPlan pl) {
         }
         g[i] = v;
     }
+    // first-layer biases, parked in the slots of the hidden vector they will be added to
+    // (a global load per hidden unit inside the loop would cost an L2 round trip each)
+    for (int m = tid; m < mid; m += kCbThreads) h[m * kSB] = ldf(reinterpret_cast<const T*>(pl.b1) + m);
     __syncthreads();
 
     // second-layer accumulators of this thread's channel (threads beyond the slice idle there)
-    const bool has_channel = tid < CW;
-    const int c = blockIdx.y * CW + (has_channel ? tid : 0);
-    float r[KK][kSB];
+    constexpr int ST = 2;                      // samples per thread in the second layer
+    const int ch = tid & (kCbSlice - 1);       // channel within the slice
+    const int s0 = (tid / kCbSlice) * ST;      // first of the thread's samples (warp-uniform)
+    const bool has_channel = ch < CW;
+    const int c = blockIdx.y * CW + (has_channel ? ch : 0);
+    float r[KK][ST];
 #pragma unroll
     for (int t = 0; t < KK; ++t) {
         const float bias = ldf(reinterpret_cast<const T*>(pl.b2) + (long long)c * KK + t);
 #pragma unroll
-        for (int s = 0; s < kSB; ++s) r[t][s] = bias;
+        for (int s = 0; s < ST; ++s) r[t][s] = bias;
     }
 
     for (int i = 0; i < n_chunks; ++i) {
@@ -181,7 +189,7 @@ channel_branch_kernel(const __grid_constant__ CbPlan pl) {
                 }
                 if (lane == 0) {
                     const int m = r0 + rr;
-                    const float bias = ldf(reinterpret_cast<const T*>(pl.b1) + m);
+                    const float bias = h[m * kSB];  // parked there before the loop
 #pragma unroll
                     for (int s = 0; s < kSB; ++s) h[m * kSB + s] = fmaxf(acc[s] + bias, 0.f);
                 }
@@ -190,16 +198,15 @@ channel_branch_kernel(const __grid_constant__ CbPlan pl) {
             // second layer: this thread's channel, the chunk's hidden units
             const int m0 = (i - pl.n_chunks_a) * pl.m_per_chunk;
             const int nm = (mid - m0) < pl.m_per_chunk ? (mid - m0) : pl.m_per_chunk;
-            uint32_t wa = base + (uint32_t)tid * ES;
+            uint32_t wa = base + (uint32_t)ch * ES;
+#pragma unroll 2
             for (int mm = 0; mm < nm; ++mm) {
-                const float4 hv = *reinterpret_cast<const float4*>(h + (m0 + mm) * kSB);
+                const float2 hv = *reinterpret_cast<const float2*>(h + (m0 + mm) * kSB + s0);
 #pragma unroll
                 for (int t = 0; t < KK; ++t) {
                     const float w = lds_elem<T>(wa + (uint32_t)(t * CW) * ES);
                     r[t][0] = fmaf(w, hv.x, r[t][0]);
                     r[t][1] = fmaf(w, hv.y, r[t][1]);
-                    r[t][2] = fmaf(w, hv.z, r[t][2]);
-                    r[t][3] = fmaf(w, hv.w, r[t][3]);
                 }
                 wa += (uint32_t)(KK * CW) * ES;
             }
@@ -217,8 +224,8 @@ channel_branch_kernel(const __grid_constant__ CbPlan pl) {
 #pragma unroll
     for (int t = 0; t < KK; ++t) gn[t] = ldf(reinterpret_cast<const T*>(pl.gain) + (long long)c * KK + t);
 #pragma unroll
-    for (int s = 0; s < kSB; ++s) {
-        if (s >= nb) break;
+    for (int s = 0; s < ST; ++s) {
+        if (s0 + s >= nb) break;
         float sum = 0.f;
 #pragma unroll
         for (int t = 0; t < KK; ++t) sum += r[t][s];
@@ -230,7 +237,7 @@ channel_branch_kernel(const __grid_constant__ CbPlan pl) {
             var = fmaf(dv, dv, var);
         }
         const float inv = 1.f / (sqrtf(var * (1.f / (KK - 1))) + 1e-10f);
-        T* o = reinterpret_cast<T*>(pl.cf) + ((long long)(b0 + s) * C + c) * KK;
+        T* o = reinterpret_cast<T*>(pl.cf) + ((long long)(b0 + s0 + s) * C + c) * KK;
 #pragma unroll
         for (int t = 0; t < KK; ++t) o[t] = (T)((r[t][s] - mean) * inv * gn[t]);
     }
@@ -238,7 +245,7 @@ channel_branch_kernel(const __grid_constant__ CbPlan pl) {
 
 template <typename T>
 static int channel_branch_launch(CbPlan& pl, int k, int device, cudaStream_t st) {
-    static_assert(kSB == 4, "the inner loop reads the hidden vector as float4");
+    static_assert(kSB == 4 && kCbThreads == 2 * kCbSlice, "two threads per channel, two samples each");
     constexpr int ES = (int)sizeof(T);
     const int KK = k * k;
     pl.rows_per_chunk = (int)(kCbChunk / ((uint32_t)pl.C * ES));
@@ -273,7 +280,7 @@ static int channel_branch_launch(CbPlan& pl, int k, int device, cudaStream_t st)
 
 extern "C" int ddf_b200_channel_filter_slice(int C) {
     // channels per slice of the re-laid-out second weight
-    return C >= ddf::kCbThreads ? ddf::kCbThreads : C;
+    return C >= ddf::kCbSlice ? ddf::kCbSlice : C;
 }
 
 extern "C" int ddf_b200_channel_filter(const float* pooled, int n_partials, float pool_scale,
