@@ -24,6 +24,7 @@ SYMBOLS = (
     "ddf_b200_launch_count", "ddf_b200_backward_noalloc", "ddf_b200_backward_noalloc_limit",
     "ddf_b200_forward_sfnorm", "ddf_b200_nhwc_to_nchw", "ddf_b200_nchw_to_nhwc",
     "ddf_b200_channel_filter", "ddf_b200_channel_filter_slice",
+    "ddf_b200_frontend_tiles", "ddf_b200_pack_frontend",
 )
 
 
@@ -56,6 +57,10 @@ def load() -> ctypes.CDLL:
         L.ddf_b200_nhwc_to_nchw.argtypes = [vp, vp] + [i] * 5 + [vp]
         L.ddf_b200_nchw_to_nhwc.restype = i
         L.ddf_b200_nchw_to_nhwc.argtypes = [vp, vp] + [i] * 5 + [vp, vp, i, vp]
+        L.ddf_b200_frontend_tiles.restype = i
+        L.ddf_b200_frontend_tiles.argtypes = [i, i]
+        L.ddf_b200_pack_frontend.restype = i
+        L.ddf_b200_pack_frontend.argtypes = [vp] * 6 + [i] * 7 + [vp]
         L.ddf_b200_channel_filter_slice.restype = i
         L.ddf_b200_channel_filter_slice.argtypes = [i]
         L.ddf_b200_channel_filter.restype = i

@@ -90,7 +90,44 @@ def build_channel_branch(in_channels, kernel_size, nonlinearity='relu', se_ratio
         FilterNorm(in_channels, kernel_size, 'channel', nonlinearity, running_std=True))
 
 
-def channel_filter_fused(branch: nn.Sequential, x: torch.Tensor, kernel_size: int):
+def pack_frontend(x: torch.Tensor, conv: nn.Conv2d | None = None):
+    """One pass over a channels_last ``x`` through ``ddf_b200_pack_frontend``: (x as contiguous
+    NCHW, the 1x1 convolution ``conv`` of x as contiguous NCHW or None when ``conv`` is None,
+    per-tile channel sums (B, NT, C) float32).  Returns None when the case is outside the
+    kernel's range or gradients are being recorded."""
+    from . import _lib
+    from .op import _DTYPES
+    if torch.is_grad_enabled() and (x.requires_grad or (conv is not None and conv.weight.requires_grad)):
+        return None
+    b, c, h, w = x.shape
+    if (not x.is_cuda or x.dtype not in _DTYPES or x.dtype == torch.float64 or x.is_contiguous()
+            or not x.is_contiguous(memory_format=torch.channels_last) or c > 2048):
+        return None
+    g, s = 0, 1
+    if conv is not None:
+        g, s = conv.out_channels, conv.stride[0]
+        if (conv.kernel_size != (1, 1) or conv.stride[0] != conv.stride[1] or conv.bias is None
+                or conv.weight.dtype != x.dtype or g > 36 or g * c * 4 > 160 * 1024
+                or h % s != 0 or w % s != 0):
+            return None
+    lib = _lib.load()
+    nt = int(lib.ddf_b200_frontend_tiles(h, w))
+    x_nchw = torch.empty((b, c, h, w), dtype=x.dtype, device=x.device)
+    pooled = torch.empty((b, nt, c), dtype=torch.float32, device=x.device)
+    raw = wsp = None
+    if conv is not None:
+        raw = torch.empty((b, g, h // s, w // s), dtype=x.dtype, device=x.device)
+        wsp = conv.weight.detach().reshape(g, c).contiguous()
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    with torch.cuda.device(x.device):
+        _lib.check(lib.ddf_b200_pack_frontend(
+            x.data_ptr(), x_nchw.data_ptr(), ptr(wsp), ptr(conv.bias if conv is not None else None),
+            ptr(raw), pooled.data_ptr(), b, c, h, w, g, s, _DTYPES[x.dtype],
+            torch.cuda.current_stream().cuda_stream))
+    return x_nchw, raw, pooled
+
+
+def channel_filter_fused(branch: nn.Sequential, x: torch.Tensor, kernel_size: int, pooled=None):
     """The channel branch (``build_channel_branch``) through the library's single kernel:
     a float32 global average pool (one torch reduction) followed by
     ``ddf_b200_channel_filter``.  Returns (B, C, k, k) in x's dtype, or None when the case
@@ -108,7 +145,11 @@ def channel_filter_fused(branch: nn.Sequential, x: torch.Tensor, kernel_size: in
             or c > 2048 or mid > 512 or not norm.runing_std or norm.runing_mean
             or any(p is None or p.dtype != x.dtype for p in params)):
         return None
-    pooled = x.mean(dim=(2, 3), dtype=torch.float32).contiguous()
+    if pooled is None:   # (B, 1, C) means; else (B, NT, C) partial sums from pack_frontend
+        pooled = x.mean(dim=(2, 3), dtype=torch.float32).contiguous()
+        n_part, pool_scale = 1, 1.0
+    else:
+        n_part, pool_scale = pooled.shape[1], 1.0 / (x.shape[2] * x.shape[3])
     out = torch.empty((b, c, kernel_size, kernel_size), dtype=x.dtype, device=x.device)
     # 1x1 weights: (out, in, 1, 1) is the same memory in contiguous and channels_last form
     w1 = conv1.weight.detach().reshape(mid, c).contiguous()
@@ -127,7 +168,7 @@ def channel_filter_fused(branch: nn.Sequential, x: torch.Tensor, kernel_size: in
     w2 = cache[1]
     with torch.cuda.device(x.device):
         _lib.check(lib.ddf_b200_channel_filter(
-            pooled.data_ptr(), 1, 1.0, w1.data_ptr(), conv1.bias.data_ptr(), w2.data_ptr(),
+            pooled.data_ptr(), n_part, pool_scale, w1.data_ptr(), conv1.bias.data_ptr(), w2.data_ptr(),
             conv2.bias.data_ptr(), norm.std.data_ptr(), out.data_ptr(), b, c, mid, kernel_size,
             _DTYPES[x.dtype], torch.cuda.current_stream().cuda_stream))
     return out
@@ -164,8 +205,17 @@ class DDFPack(nn.Module):
         # still consume the tensor as it came (their convolutions want that layout) and
         # only the op's operands are converted, by the library's transpose kernel.
         x_in = x
-        x = to_nchw(x)
-        channel_filter = channel_filter_fused(self.channel_branch, x_in, k) if self.fuse_channel_branch else None
+        front = None
+        if self.fuse_channel_branch:
+            # channels_last inference: the transpose to NCHW also leaves the channel branch's
+            # pooled sums.  (The kernel can do the spatial 1x1 convolution in the same pass,
+            # but on CUDA cores that is slower than the library's tensor-core convolution.)
+            front = pack_frontend(x_in)
+        x = front[0] if front is not None else to_nchw(x)
+        channel_filter = None
+        if self.fuse_channel_branch:
+            channel_filter = channel_filter_fused(self.channel_branch, x_in, k,
+                                                  front[2] if front is not None else None)
         if channel_filter is None:
             channel_filter = self.channel_branch(x_in)
         channel_filter = channel_filter.reshape(b * g, c // g, k, k).contiguous()
