@@ -513,6 +513,7 @@ def run_model(args, rank, world, local_rank):
         model = model.to(memory_format=torch.channels_last)
     for m in model.ddf_layers():
         m.fuse_filter_norm = not args.unfused_norm
+        m.fuse_channel_branch = not args.unfused_norm
     g = torch.Generator().manual_seed(1)
     x = torch.randn(gbatch, 3, 224, 224, generator=g)[lo:hi].to(dev, dtype)
     if args.channels_last:
@@ -564,7 +565,8 @@ def run_model(args, rank, world, local_rank):
             "vs_baseline": None, "dtype": str(dtype).replace("torch.", ""), "data": "synthetic",
             "config": {"workload": f"{name} inference, global batch {gbatch}, 224x224, random init",
                        "per_gpu_batch": hi - lo, "cuda_graph": graphed,
-                       "spatial_filter_norm": "separate torch ops" if args.unfused_norm else "fused into the DDF kernel",
+                       "filter_branches": "reference module sequence (torch ops)" if args.unfused_norm
+                       else "spatial FilterNorm fused into the DDF kernel, channel branch as one kernel",
                        "memory_format": "channels_last around the DDF layers" if args.channels_last else "NCHW",
                        "batchnorm": {None: "as built", "plain": "folded into the preceding convolutions",
                                      "fused": "folded; conv+bias(+shortcut)+ReLU as single cuDNN calls"}[args.fold_bn]},
@@ -646,7 +648,8 @@ def main():
                     help="op workload: skip the per-call timings and the CPU baseline (scaling runs)")
     ap.add_argument("--no-graph", action="store_true", help="model workload: eager launches")
     ap.add_argument("--unfused-norm", action="store_true",
-                    help="model workload: run the spatial FilterNorm as separate torch ops, as the reference does")
+                    help="model workload: run both filter branches as the reference's module sequence "
+                         "(FilterNorm and the channel branch as separate torch ops)")
     ap.add_argument("--channels-last", action="store_true",
                     help="model workload: convolutions in channels_last; each DDFPack converts to NCHW and back")
     ap.add_argument("--fold-bn", nargs="?", const="plain", default=None, choices=["plain", "fused"],
