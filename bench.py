@@ -423,6 +423,47 @@ def run_backward(args, rank, world, local_rank):
                     total_bytes += nb
                     total_us += us
                 del sets
+    # The sweep's own shapes (bf16, mul, k = 3), not part of `value`: which of them the
+    # streaming backward covers and what the others cost on the generic kernels.
+    shape_rows = []
+    for (C2, H2, s2) in SHAPES:
+        k, d, dtc, dtype, es = 3, 1, _lib.BF16, torch.bfloat16, 2
+        oh = H2 // s2
+        g = torch.Generator().manual_seed(700 + C2 + s2)
+        base = (torch.randn(B, C2, oh, oh, generator=g), torch.randn(B, C2, H2, H2, generator=g).relu_(),
+                torch.randn(B, C2, k, k, generator=g) / 3, torch.randn(B, k * k, oh, oh, generator=g) / 3)
+        nb = es * (B * C2 * oh * oh + 2 * B * C2 * H2 * H2 + 2 * B * C2 * k * k + 2 * B * k * k * oh * oh)
+        nsets = max(3, (2 * L2_BYTES) // nb + 2)
+        sets = []
+        for _ in range(nsets):
+            go, x, cf, sf = (t.to(dev, dtype) for t in base)
+            sets.append((go, x, cf, sf, torch.empty_like(x), torch.empty_like(cf), torch.empty_like(sf)))
+        wsb = int(L.ddf_b200_backward_workspace(B, C2, H2, H2, k, d, s2, _lib.MUL, dtc, _lib.VARIANT_AUTO))
+        ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=dev)
+
+        def call2(st):
+            go, x, cf, sf, gx, gcf, gsf = st
+            _lib.check(L.ddf_b200_backward(
+                go.data_ptr(), x.data_ptr(), cf.data_ptr(), sf.data_ptr(), gx.data_ptr(), gcf.data_ptr(),
+                gsf.data_ptr(), ws.data_ptr(), wsb, B, C2, H2, H2, k, d, s2, _lib.MUL, dtc,
+                _lib.VARIANT_AUTO, torch.cuda.current_stream().cuda_stream))
+
+        for st in sets:
+            call2(st)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(2):
+            for st in sets:
+                call2(st)
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / (2 * nsets)
+        shape_rows.append({"C": C2, "H": H2, "stride": s2, "us": round(us, 1), "gbs": round(nb / us / 1e3, 1),
+                           "frac": round(nb / us / 1e3 / peak, 4),
+                           "filter_gradients": "streaming" if wsb > 0 else "generic",
+                           "grad_x": "streaming" if s2 == 1 else "generic"})
+        del sets
     if rank == 0:
         print(json.dumps({
             "metric": "ddf_backward_hbm_gbs", "value": round(total_bytes / total_us / 1e3, 1), "unit": "GB/s",
@@ -431,7 +472,8 @@ def run_backward(args, rank, world, local_rank):
             "dtype": "f32+bf16 I/O, f32 arithmetic", "data": "synthetic",
             "config": {"workload": "configs[2]: DDF backward, B=64, C=256, 28x28, k 3/5, d 1/2, mul/add",
                        "l2": "rotating buffer sets larger than L2"},
-            "peak": peak, "peak_kind": f"of {peak_kind}", "per_case": rows}))
+            "peak": peak, "peak_kind": f"of {peak_kind}", "per_case": rows,
+            "sweep_shapes_bf16_mul_B64": shape_rows}))
 
 
 def run_sfnorm(args, rank, world, local_rank):

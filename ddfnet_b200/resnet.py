@@ -167,6 +167,12 @@ def fold_batchnorm(model: "DDFResNet", fuse_activations: bool = False) -> "DDFRe
             m.conv3, m.bn3 = _fold(m.conv3, m.bn3), nn.Identity()
             if m.downsample is not None:
                 m.downsample = nn.Sequential(_fold(m.downsample[0], m.downsample[1]))
+                if fuse_activations:
+                    # relu(conv3(x) + b3 + (conv_d(s) + b_d)): one bias instead of two, and no
+                    # separate bias-add kernel over the widest tensor of the block
+                    with torch.no_grad():
+                        m.conv3.bias.add_(m.downsample[0].bias)
+                    m.downsample[0].bias = None
     return model
 
 
