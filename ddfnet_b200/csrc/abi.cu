@@ -109,6 +109,19 @@ static int generic_forward_launch(const Problem& p, const void* x, const void* c
 template <typename T>
 static int generic_grad_x_launch(const Problem& p, const void* go, const void* cf, const void* sf,
                                  void* gx, int sm_count, cudaStream_t st) {
+    // the down-sampling layers' case has a kernel of its own (no per-tap divisions)
+    if (p.k == 3 && p.d == 1 && p.s == 2 && p.H == 2 * p.OH && p.W == 2 * p.OW && p.B <= 65535) {
+        constexpr int CH = 16;
+        dim3 grid((unsigned)((p.OH * p.OW + 255) / 256), (unsigned)((p.C + CH - 1) / CH), (unsigned)p.B);
+        if (grid.y <= 65535u) {
+            if (p.combine == DDF_B200_MUL)
+                grad_x_k3s2<T, DDF_B200_MUL, CH><<<grid, 256, 0, st>>>((const T*)go, (const T*)cf, (const T*)sf, (T*)gx, p);
+            else
+                grad_x_k3s2<T, DDF_B200_ADD, CH><<<grid, 256, 0, st>>>((const T*)go, (const T*)cf, (const T*)sf, (T*)gx, p);
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            return (int)cudaGetLastError();
+        }
+    }
     const long long total = (long long)p.B * p.C * p.H * p.W;
     const int grid = grid_for(total, 256, sm_count);
     if (p.combine == DDF_B200_MUL)

@@ -10,11 +10,14 @@ namespace ddf {
 static int bwd_pixels(const Problem& p, int sm_count, BwdGeometry& g) {
     if (p.dtype == DDF_B200_F64) return 0;
     const int k = p.k, d = p.d, s = p.s;
-    static const int cand[3] = {4, 2, 1};
-    for (int ci = 0; ci < 3; ++ci) {
+    // 8 comes last: it is the two-launch form, used only where no smaller P fits a plane
+    // into one CTA's threads
+    static const int cand[4] = {4, 2, 1, 8};
+    for (int ci = 0; ci < 4; ++ci) {
         const int P = cand[ci];
         bool built = false;
-        if (k == 3 && d == 1) built = (s == 1 || s == 2);
+        if (P == 8) built = (k == 3 && d == 1 && s == 1);
+        else if (k == 3 && d == 1) built = (s == 1 || s == 2);
         else if (k == 3 && d == 2 && s == 1) built = P >= 2;
         else if (k == 5 && (d == 1 || d == 2) && s == 1) built = P == 2;
         if (!built) continue;

@@ -100,13 +100,18 @@ __device__ __forceinline__ int butterfly_slot(int lane) {
     return cnt > 0 ? first : -1;
 }
 
-template <typename T, int K, int D, int S, int P, int MODE>
+// WHICH: 0 = both gradients in one pass; 1 = grad-cf only; 2 = grad-sf only.  The two
+// single-gradient forms need half the registers (either the spatial-filter values or the
+// grad-sf accumulators), which is what lets a thread own 8 pixels and a CTA's threads cover
+// a 56 x 56 plane; the launcher then runs them one after the other.
+template <typename T, int K, int D, int S, int P, int MODE, int WHICH>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
     using G = Geo<T, K, D, S, P>;
     constexpr int KK = G::KK;
     constexpr int ES = G::ES;
     constexpr bool MUL = MODE == DDF_B200_MUL;
+    constexpr bool DO_CF = WHICH != 2, DO_SF = WHICH != 1;
     // values folded per butterfly: all taps at once for k = 3, one tap row for k = 5
     constexpr int GROUP = (K == 3) ? KK : K;
     constexpr int ROWS_PER_GROUP = GROUP / K;
@@ -313,18 +318,20 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
     // for free; float elements arrive in load order and pairing them costs moves.)
     constexpr bool PK = P >= 2 && sizeof(T) == 2;
     constexpr int HP = PK ? P / 2 : 1;
-    float sfr[(MUL && !PK) ? KK : 1][PK ? 1 : P];
-    float gsf[PK ? 1 : KK][PK ? 1 : P];
-    unsigned long long sf2[(MUL && PK) ? KK : 1][HP];
-    unsigned long long gsf2[PK ? KK : 1][HP];
+    float sfr[(MUL && !PK && DO_CF) ? KK : 1][(PK || !DO_CF) ? 1 : P];
+    float gsf[(PK || !DO_SF) ? 1 : KK][(PK || !DO_SF) ? 1 : P];
+    unsigned long long sf2[(MUL && PK && DO_CF) ? KK : 1][DO_CF ? HP : 1];
+    unsigned long long gsf2[(PK && DO_SF) ? KK : 1][DO_SF ? HP : 1];
+    if constexpr (DO_SF) {
 #pragma unroll
-    for (int t = 0; t < KK; ++t) {
-        if constexpr (PK) {
+        for (int t = 0; t < KK; ++t) {
+            if constexpr (PK) {
 #pragma unroll
-            for (int q2 = 0; q2 < HP; ++q2) gsf2[t][q2] = 0ull;
-        } else {
+                for (int q2 = 0; q2 < HP; ++q2) gsf2[t][q2] = 0ull;
+            } else {
 #pragma unroll
-            for (int pp = 0; pp < P; ++pp) gsf[t][pp] = 0.f;
+                for (int pp = 0; pp < P; ++pp) gsf[t][pp] = 0.f;
+            }
         }
     }
 
@@ -335,6 +342,7 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
     const long long opl = (long long)pl.OH * pl.OW;
 
     auto flush = [&](long long sample) {
+        if constexpr (DO_SF) {
         if (pl.scratch != nullptr && active) {
             float* dst = pl.scratch + (((sample + blockIdx.x) * NP + pip) * KK) * opl +
                          (long long)oy * pl.OW + ox0;
@@ -370,6 +378,7 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
                 for (int pp = 0; pp < P; ++pp) gsf[t][pp] = 0.f;
             }
         }
+        }
     };
 
     int slot = -1;
@@ -401,7 +410,7 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
                     const uint32_t sfs =
                         sbase + pl.off_sf + (uint32_t)(((unsigned long long)b * pl.sf_bytes) & 15ull);
 #pragma unroll
-                    for (int t = 0; t < KK; ++t) {
+                    for (int t = 0; t < (DO_CF ? KK : 0); ++t) {
                         const uint32_t a = sfs + (uint32_t)(((t * pl.OH + oy) * pl.OW + ox0) * ES);
                         if constexpr (G::OUTB < 4) {
                             sfr[t][0] = Word<T>::get(lds16(a), 0);
@@ -465,50 +474,53 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
                         const int u = ii * K + j;
                         if constexpr (PK) {
                             unsigned long long c2 = 0ull;
-                            if constexpr (MUL) c2 = lds64_pair(cfc_s + 8u * t);
+                            if constexpr (MUL && DO_SF) c2 = lds64_pair(cfc_s + 8u * t);
 #pragma unroll
                             for (int q2 = 0; q2 < HP; ++q2) {
                                 const unsigned long long prod2 =
                                     f2_mul(g2[q2], f2_pack(xr[q2 * S + j * D], xr[(q2 + HP) * S + j * D]));
                                 if constexpr (MUL) {
-                                    gsf2[t][q2] = f2_fma(prod2, c2, gsf2[t][q2]);
-                                    part2[u] = f2_fma(prod2, sf2[t][q2], part2[u]);
+                                    if constexpr (DO_SF) gsf2[t][q2] = f2_fma(prod2, c2, gsf2[t][q2]);
+                                    if constexpr (DO_CF) part2[u] = f2_fma(prod2, sf2[t][q2], part2[u]);
                                 } else {
-                                    gsf2[t][q2] = f2_add(gsf2[t][q2], prod2);
-                                    part2[u] = f2_add(part2[u], prod2);
+                                    if constexpr (DO_SF) gsf2[t][q2] = f2_add(gsf2[t][q2], prod2);
+                                    if constexpr (DO_CF) part2[u] = f2_add(part2[u], prod2);
                                 }
                             }
                         } else {
                             float c = 1.f;
-                            if constexpr (MUL) c = ldsf(cfc_s + 8u * t);
+                            if constexpr (MUL && DO_SF) c = ldsf(cfc_s + 8u * t);
 #pragma unroll
                             for (int pp = 0; pp < P; ++pp) {
                                 const float prod = g[pp] * xr[pp * S + j * D];
                                 if constexpr (MUL) {
-                                    gsf[t][pp] = fmaf(prod, c, gsf[t][pp]);
-                                    part[u] = fmaf(prod, sfr[t][pp], part[u]);
+                                    if constexpr (DO_SF) gsf[t][pp] = fmaf(prod, c, gsf[t][pp]);
+                                    if constexpr (DO_CF) part[u] = fmaf(prod, sfr[t][pp], part[u]);
                                 } else {
-                                    gsf[t][pp] += prod;
-                                    part[u] += prod;
+                                    if constexpr (DO_SF) gsf[t][pp] += prod;
+                                    if constexpr (DO_CF) part[u] += prod;
                                 }
                             }
                         }
                     }
                 }
-                if constexpr (PK) {
+                if constexpr (DO_CF) {
+                    if constexpr (PK) {
 #pragma unroll
-                    for (int u = 0; u < GROUP; ++u) {
-                        float lo, hi;
-                        f2_unpack(part2[u], lo, hi);
-                        part[u] = lo + hi;
+                        for (int u = 0; u < GROUP; ++u) {
+                            float lo, hi;
+                            f2_unpack(part2[u], lo, hi);
+                            part[u] = lo + hi;
+                        }
                     }
-                }
-                if (!active) {
+                    if (!active) {
 #pragma unroll
-                    for (int u = 0; u < GROUP; ++u) part[u] = 0.f;
+                        for (int u = 0; u < GROUP; ++u) part[u] = 0.f;
+                    }
+                    butterfly_reduce<GROUP>(part, lane);
+                    if (my_slot >= 0)
+                        sts32(gpart_s + 4u * (uint32_t)(i0 * K + my_slot), __float_as_uint(part[0]));
                 }
-                butterfly_reduce<GROUP>(part, lane);
-                if (my_slot >= 0) sts32(gpart_s + 4u * (uint32_t)(i0 * K + my_slot), __float_as_uint(part[0]));
             }
 
             xplane_s += (uint32_t)NP * pl.xplane_bytes;
@@ -688,14 +700,14 @@ bool make_bwd_plan(const BwdArgs& a, BwdPlan& pl, uint32_t& smem_bytes, BwdGeome
     return true;
 }
 
-template <typename T, int K, int D, int S, int P, int MODE>
+template <typename T, int K, int D, int S, int P, int MODE, int WHICH = 0>
 int bwd_launch(const BwdArgs& a, cudaStream_t stream, int* launches) {
     BwdPlan pl;
     BwdGeometry g;
     uint32_t smem = 0;
     if (!make_bwd_plan<T, K, D, S, P>(a, pl, smem, g)) return kNotHandled;
     if (a.gsf && !a.workspace) return DDF_B200_E_WORKSPACE;
-    auto kern = bwd_filters_kernel<T, K, D, S, P, MODE>;
+    auto kern = bwd_filters_kernel<T, K, D, S, P, MODE, WHICH>;
     static std::atomic<unsigned long long> opted_in{0};
     const unsigned long long bit = 1ull << (a.device & 63);
     if (!(opted_in.load(std::memory_order_acquire) & bit)) {
@@ -718,6 +730,24 @@ int bwd_launch(const BwdArgs& a, cudaStream_t stream, int* launches) {
                               a.p.B, a.p.C, g.NP, n, g.total_passes, g.grid);
         if (e != cudaSuccess) return (int)e;
         ++*launches;
+    }
+    return 0;
+}
+
+// The two gradients as two launches of the single-gradient forms (8 pixels per thread).
+template <typename T, int K, int D, int S, int P, int MODE>
+int bwd_launch_split(const BwdArgs& a, cudaStream_t stream, int* launches) {
+    if (a.gcf) {
+        BwdArgs one = a;
+        one.gsf = nullptr;
+        const int rc = bwd_launch<T, K, D, S, P, MODE, 1>(one, stream, launches);
+        if (rc) return rc;
+    }
+    if (a.gsf) {
+        BwdArgs one = a;
+        one.gcf = nullptr;
+        const int rc = bwd_launch<T, K, D, S, P, MODE, 2>(one, stream, launches);
+        if (rc) return rc;
     }
     return 0;
 }

@@ -74,6 +74,63 @@ generic_forward(const T* __restrict__ x, const T* __restrict__ cf, const T* __re
     }
 }
 
+// grad-x for k = 3, dilation 1, stride 2, even H and W (H = 2*OH, W = 2*OW): the case of the
+// down-sampling layers.  A thread owns one OUTPUT pixel q = (qy, qx) of a sample and walks a
+// chunk of channels; per channel it writes the 2 x 2 input pixels (2qy.., 2qx..).  With stride
+// 2 each input pixel receives only the taps whose offset has its parity -- 1, 2, 2 and 4 of
+// the nine -- so the four results need exactly nine products, and the nine spatial-filter
+// values they use (at q and its right / lower / lower-right neighbours) stay in registers for
+// all channels:
+//   gx[2qy  ][2qx  ] = go[q]*w4[q]
+//   gx[2qy  ][2qx+1] = go[q]*w5[q]  + go[q+x]*w3[q+x]
+//   gx[2qy+1][2qx  ] = go[q]*w7[q]  + go[q+y]*w1[q+y]
+//   gx[2qy+1][2qx+1] = go[q]*w8[q]  + go[q+x]*w6[q+x] + go[q+y]*w2[q+y] + go[q+x+y]*w0[q+x+y]
+// (w_t[q] = cf[c,t] (.) sf[t,q]; neighbours outside the plane contribute nothing).
+// Same arithmetic as generic_grad_x, without its per-tap divisions and parity tests.
+template <typename T, int MODE, int CH>
+__global__ void __launch_bounds__(256)
+grad_x_k3s2(const T* __restrict__ go, const T* __restrict__ cf, const T* __restrict__ sf,
+            T* __restrict__ gx, Problem p) {
+    using A = typename Elem<T>::acc_t;
+    const int q = blockIdx.x * blockDim.x + threadIdx.x;
+    const int opl = p.OH * p.OW;
+    if (q >= opl) return;
+    const int qy = q / p.OW, qx = q - qy * p.OW;
+    const long long b = blockIdx.z;
+    const bool has_x = qx + 1 < p.OW, has_y = qy + 1 < p.OH;
+    const T* sfb = sf + b * 9 * (long long)opl + q;
+    auto sfv = [&](int t, int off, bool ok) -> A { return ok ? (A)Elem<T>::load(sfb + (long long)t * opl + off) : (A)0; };
+    const A s4 = sfv(4, 0, true), s5 = sfv(5, 0, true), s7 = sfv(7, 0, true), s8 = sfv(8, 0, true);
+    const A s3 = sfv(3, 1, has_x), s6 = sfv(6, 1, has_x);
+    const A s1 = sfv(1, p.OW, has_y), s2 = sfv(2, p.OW, has_y);
+    const A s0 = sfv(0, p.OW + 1, has_x && has_y);
+    const int c_lo = blockIdx.y * CH;
+    const int c_hi = c_lo + CH < p.C ? c_lo + CH : p.C;
+    const long long ipl = (long long)p.H * p.W;
+    for (int c = c_lo; c < c_hi; ++c) {
+        const long long plane = b * p.C + c;
+        const T* gop = go + plane * opl + q;
+        const T* cfp = cf + plane * 9;
+        A w[9];
+#pragma unroll
+        for (int t = 0; t < 9; ++t) w[t] = Elem<T>::load(cfp + t);
+        const A g00 = Elem<T>::load(gop);
+        const A g01 = has_x ? (A)Elem<T>::load(gop + 1) : (A)0;
+        const A g10 = has_y ? (A)Elem<T>::load(gop + p.OW) : (A)0;
+        const A g11 = (has_x && has_y) ? (A)Elem<T>::load(gop + p.OW + 1) : (A)0;
+        const A r00 = g00 * combine_w<MODE, A>(w[4], s4);
+        const A r01 = g00 * combine_w<MODE, A>(w[5], s5) + g01 * combine_w<MODE, A>(w[3], s3);
+        const A r10 = g00 * combine_w<MODE, A>(w[7], s7) + g10 * combine_w<MODE, A>(w[1], s1);
+        const A r11 = g00 * combine_w<MODE, A>(w[8], s8) + g01 * combine_w<MODE, A>(w[6], s6) +
+                      g10 * combine_w<MODE, A>(w[2], s2) + g11 * combine_w<MODE, A>(w[0], s0);
+        T* o = gx + plane * ipl + (long long)(2 * qy) * p.W + 2 * qx;
+        Elem<T>::store(o, r00);
+        Elem<T>::store(o + 1, r01);
+        Elem<T>::store(o + p.W, r10);
+        Elem<T>::store(o + p.W + 1, r11);
+    }
+}
+
 // gx[b,c,py,px] = sum_t go[b,c,q] * w(cf[b,c,t], sf[b,t,q]),  q*s + off_t = p.
 // Replaces DDFBackward_Feature (ddf/src/cuda/ddf_mul_cuda_kernel.cu:198-290)
 // and the two transposes around it (:433-443, :463-473).

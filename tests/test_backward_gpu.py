@@ -37,7 +37,9 @@ for k, d in [(1, 1), (3, 1), (3, 2), (5, 1), (5, 2), (7, 1)]:
         GENERIC.append((2, 3, 9, 11, k, d, s))
 GENERIC += [(1, 70, 10, 10, 3, 1, 1), (35, 1, 10, 10, 3, 2, 2), (1, 1, 50, 50, 3, 1, 1),
             (1, 70, 10, 10, 5, 1, 2), (20, 1, 10, 10, 5, 2, 1), (1, 1, 40, 40, 5, 1, 1),
-            (2, 5, 13, 9, 3, 1, 2), (1, 2, 4, 30, 3, 1, 3)]
+            (2, 5, 13, 9, 3, 1, 2), (1, 2, 4, 30, 3, 1, 3),
+            # even planes at k=3, d=1, s=2: the dedicated stride-2 grad-x kernel
+            (2, 5, 12, 10, 3, 1, 2), (1, 20, 6, 8, 3, 1, 2), (3, 17, 14, 14, 3, 1, 2), (1, 3, 2, 2, 3, 1, 2)]
 
 
 @pytest.mark.parametrize("shape", GENERIC)
