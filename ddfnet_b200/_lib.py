@@ -22,7 +22,7 @@ SYMBOLS = (
     "ddf_b200_version", "ddf_b200_strerror", "ddf_b200_forward", "ddf_b200_plan",
     "ddf_b200_backward_workspace", "ddf_b200_backward", "ddf_b200_take_fault",
     "ddf_b200_launch_count", "ddf_b200_backward_noalloc", "ddf_b200_backward_noalloc_limit",
-    "ddf_b200_forward_sfnorm", "ddf_b200_nhwc_to_nchw", "ddf_b200_nchw_to_nhwc",
+    "ddf_b200_forward_sfnorm", "ddf_b200_nhwc_to_nchw", "ddf_b200_nchw_to_nhwc", "ddf_b200_nhwc_to_nchw_affine",
     "ddf_b200_channel_filter", "ddf_b200_channel_filter_slice",
     "ddf_b200_frontend_tiles", "ddf_b200_pack_frontend",
 )
@@ -55,6 +55,8 @@ def load() -> ctypes.CDLL:
         L.ddf_b200_forward_sfnorm.argtypes = [vp] * 4 + [i] * 10 + [ctypes.c_double, vp]
         L.ddf_b200_nhwc_to_nchw.restype = i
         L.ddf_b200_nhwc_to_nchw.argtypes = [vp, vp] + [i] * 5 + [vp]
+        L.ddf_b200_nhwc_to_nchw_affine.restype = i
+        L.ddf_b200_nhwc_to_nchw_affine.argtypes = [vp, vp] + [i] * 6 + [vp, vp, i, vp]
         L.ddf_b200_nchw_to_nhwc.restype = i
         L.ddf_b200_nchw_to_nhwc.argtypes = [vp, vp] + [i] * 5 + [vp, vp, i, vp]
         L.ddf_b200_frontend_tiles.restype = i

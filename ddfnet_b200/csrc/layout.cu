@@ -53,21 +53,23 @@ __device__ __forceinline__ void store4(T* p, bool vec, int n_valid, const T (&in
 
 // TO_NHWC = true : src (B,C,HW) -> dst (B,HW,C), optional dst = relu(src * scale[c] + shift[c])
 // TO_NHWC = false: src (B,HW,C) -> dst (B,C,HW)
+// SC: channels per pixel in the NHWC SOURCE of the TO_NHWC = false direction (>= C; only the
+// first C are taken, e.g. a convolution padded to a friendlier channel count); = C otherwise.
 template <typename T, bool TO_NHWC>
 __global__ void __launch_bounds__(256)
-layout_kernel(const T* __restrict__ src, T* __restrict__ dst, int C, int HW,
+layout_kernel(const T* __restrict__ src, T* __restrict__ dst, int C, int HW, int SC,
               const float* __restrict__ scale, const float* __restrict__ shift, int relu) {
     constexpr int PITCH = kTile + (sizeof(T) == 2 ? 2 : 1);
     __shared__ T tile[kTile][PITCH];  // [channel][pixel]
     const int t = threadIdx.x;
     const int p0 = blockIdx.x * kTile, c0 = blockIdx.y * kTile;
     const long long b = blockIdx.z;
-    const T* s = src + b * (long long)C * HW;
+    const T* s = src + b * (long long)(TO_NHWC ? C : SC) * HW;
     T* d = dst + b * (long long)C * HW;
     const int sub = t >> 4;        // 0..15: row within a pass
     const int q = (t & 15) * 4;    // first of the thread's four elements along the row
     // 8-byte (2-byte types) or 16-byte (float) accesses need rows that keep that alignment.
-    const bool vec_hw = (HW % 4) == 0, vec_c = (C % 4) == 0;
+    const bool vec_hw = (HW % 4) == 0, vec_c = (C % 4) == 0, vec_sc = (SC % 4) == 0;
 
     if (TO_NHWC) {
 #pragma unroll
@@ -109,7 +111,20 @@ layout_kernel(const T* __restrict__ src, T* __restrict__ dst, int C, int HW,
             const int p = p0 + r * 16 + sub, c = c0 + q;
             if (p < HW && c < C) {
                 T v[4];
-                load4(s + (long long)p * C + c, vec_c, C - c < 4 ? C - c : 4, v);
+                load4(s + (long long)p * SC + c, vec_sc, C - c < 4 ? C - c : 4, v);
+                if (scale != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (c + i < C) {
+                            float f = fmaf((float)v[i], scale[c + i], shift[c + i]);
+                            if (relu) f = fmaxf(f, 0.f);
+                            v[i] = (T)f;
+                        }
+                    }
+                } else if (relu) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) v[i] = (T)fmaxf((float)v[i], 0.f);
+                }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) tile[q + i][r * 16 + sub] = v[i];
             }
@@ -129,7 +144,7 @@ layout_kernel(const T* __restrict__ src, T* __restrict__ dst, int C, int HW,
 }
 
 template <typename T, bool TO_NHWC>
-static int layout_launch(const void* src, void* dst, int B, int C, int HW, const float* scale,
+static int layout_launch(const void* src, void* dst, int B, int C, int HW, int SC, const float* scale,
                          const float* shift, int relu, cudaStream_t st) {
     // The vector accesses also need 8- / 16-byte aligned bases.
     const uintptr_t mask = sizeof(T) * 4 - 1;
@@ -137,25 +152,25 @@ static int layout_launch(const void* src, void* dst, int B, int C, int HW, const
         return DDF_B200_E_UNSUPPORTED;
     dim3 grid((unsigned)((HW + kTile - 1) / kTile), (unsigned)((C + kTile - 1) / kTile), (unsigned)B);
     if (grid.y > 65535u || grid.z > 65535u) return DDF_B200_E_TOO_LARGE;
-    layout_kernel<T, TO_NHWC><<<grid, 256, 0, st>>>((const T*)src, (T*)dst, C, HW, scale, shift, relu);
+    layout_kernel<T, TO_NHWC><<<grid, 256, 0, st>>>((const T*)src, (T*)dst, C, HW, SC, scale, shift, relu);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }
 
 template <bool TO_NHWC>
-static int layout_any(const void* src, void* dst, int B, int C, int H, int W, int dtype,
+static int layout_any(const void* src, void* dst, int B, int C, int H, int W, int SC, int dtype,
                       const float* scale, const float* shift, int relu, void* stream) {
     if (!src || !dst) return DDF_B200_E_NULL;
-    if (B < 1 || C < 1 || H < 1 || W < 1) return DDF_B200_E_SHAPE;
+    if (B < 1 || C < 1 || H < 1 || W < 1 || SC < C) return DDF_B200_E_SHAPE;
     if ((long long)H * W > (1ll << 30)) return DDF_B200_E_TOO_LARGE;
     if ((scale == nullptr) != (shift == nullptr)) return DDF_B200_E_NULL;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const int HW = H * W;
     switch (dtype) {
-        case DDF_B200_F32: return layout_launch<float, TO_NHWC>(src, dst, B, C, HW, scale, shift, relu, st);
-        case DDF_B200_F16: return layout_launch<__half, TO_NHWC>(src, dst, B, C, HW, scale, shift, relu, st);
+        case DDF_B200_F32: return layout_launch<float, TO_NHWC>(src, dst, B, C, HW, SC, scale, shift, relu, st);
+        case DDF_B200_F16: return layout_launch<__half, TO_NHWC>(src, dst, B, C, HW, SC, scale, shift, relu, st);
         case DDF_B200_BF16:
-            return layout_launch<__nv_bfloat16, TO_NHWC>(src, dst, B, C, HW, scale, shift, relu, st);
+            return layout_launch<__nv_bfloat16, TO_NHWC>(src, dst, B, C, HW, SC, scale, shift, relu, st);
         default: return DDF_B200_E_DTYPE;
     }
 }
@@ -166,12 +181,19 @@ extern "C" {
 
 int ddf_b200_nhwc_to_nchw(const void* src, void* dst, int B, int C, int H, int W, int dtype,
                           void* stream) {
-    return ddf::layout_any<false>(src, dst, B, C, H, W, dtype, nullptr, nullptr, 0, stream);
+    return ddf::layout_any<false>(src, dst, B, C, H, W, C, dtype, nullptr, nullptr, 0, stream);
+}
+
+int ddf_b200_nhwc_to_nchw_affine(const void* src, void* dst, int B, int C, int H, int W,
+                                 int src_channels, int dtype, const float* ch_scale,
+                                 const float* ch_shift, int relu, void* stream) {
+    return ddf::layout_any<false>(src, dst, B, C, H, W, src_channels, dtype, ch_scale, ch_shift, relu,
+                                  stream);
 }
 
 int ddf_b200_nchw_to_nhwc(const void* src, void* dst, int B, int C, int H, int W, int dtype,
                           const float* ch_scale, const float* ch_shift, int relu, void* stream) {
-    return ddf::layout_any<true>(src, dst, B, C, H, W, dtype, ch_scale, ch_shift, relu, stream);
+    return ddf::layout_any<true>(src, dst, B, C, H, W, C, dtype, ch_scale, ch_shift, relu, stream);
 }
 
 }  // extern "C"

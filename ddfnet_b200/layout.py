@@ -31,6 +31,23 @@ def to_nchw(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def to_nchw_affine(x: torch.Tensor, channels: int, scale: torch.Tensor, shift: torch.Tensor,
+                   relu: bool = False) -> torch.Tensor:
+    """Contiguous NCHW tensor of the first ``channels`` channels of a channels_last ``x``, with
+    ``x * scale[c] + shift[c]`` (float32 tensors of ``channels`` values) applied on the way."""
+    b, sc, h, w = x.shape
+    assert channels <= sc and scale.numel() == channels and shift.numel() == channels
+    if not (_native(x) and x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous()):
+        y = x[:, :channels] * scale.to(x.dtype).reshape(1, -1, 1, 1) + shift.to(x.dtype).reshape(1, -1, 1, 1)
+        return (torch.relu(y) if relu else y).contiguous()
+    out = torch.empty((b, channels, h, w), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().ddf_b200_nhwc_to_nchw_affine(
+            x.data_ptr(), out.data_ptr(), b, channels, h, w, sc, _DTYPES[x.dtype],
+            scale.data_ptr(), shift.data_ptr(), int(relu), torch.cuda.current_stream().cuda_stream))
+    return out
+
+
 def to_channels_last(x: torch.Tensor, scale: torch.Tensor | None = None,
                      shift: torch.Tensor | None = None, relu: bool = False) -> torch.Tensor:
     """channels_last copy of a contiguous NCHW tensor, optionally with

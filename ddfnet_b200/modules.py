@@ -13,7 +13,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch.nn.init import calculate_gain
 
-from .layout import to_nchw
+from .layout import to_nchw, to_nchw_affine
 from .op import ddf, ddf_sfnorm
 
 
@@ -127,6 +127,34 @@ def pack_frontend(x: torch.Tensor, conv: nn.Conv2d | None = None):
     return x_nchw, raw, pooled
 
 
+def spatial_raw_padded(conv: nn.Conv2d, x: torch.Tensor):
+    """The spatial branch's 1x1 convolution for channels_last inference: the library
+    convolution with its head*k*k output maps zero-padded to a multiple of 16 (several times
+    faster than with 9 maps) and no bias, then the library transpose that drops the padding
+    and adds the bias.  Returns contiguous NCHW (B, G, H', W'), or None when not applicable."""
+    if torch.is_grad_enabled() and (x.requires_grad or conv.weight.requires_grad):
+        return None
+    if (not x.is_cuda or x.is_contiguous() or not x.is_contiguous(memory_format=torch.channels_last)
+            or conv.kernel_size != (1, 1) or conv.bias is None or x.dtype == torch.float64
+            or conv.weight.dtype != x.dtype):
+        return None
+    g, c = conv.out_channels, conv.in_channels
+    gp = (g + 15) // 16 * 16
+    key = (conv.weight.data_ptr(), conv.weight._version, conv.bias.data_ptr(), conv.bias._version,
+           conv.weight.dtype)
+    cache = getattr(conv, "_ddf_padded", None)
+    if cache is None or cache[0] != key:
+        w = torch.zeros((gp, c, 1, 1), dtype=conv.weight.dtype, device=conv.weight.device)
+        w[:g] = conv.weight.detach()
+        w = w.contiguous(memory_format=torch.channels_last)
+        cache = (key, w, torch.ones(g, dtype=torch.float32, device=w.device),
+                 conv.bias.detach().float().contiguous())
+        conv._ddf_padded = cache
+    _, w, ones, bias = cache
+    y = F.conv2d(x, w, None, conv.stride)
+    return to_nchw_affine(y, g, ones, bias)
+
+
 def channel_filter_fused(branch: nn.Sequential, x: torch.Tensor, kernel_size: int, pooled=None):
     """The channel branch (``build_channel_branch``) through the library's single kernel:
     a float32 global average pool (one torch reduction) followed by
@@ -221,7 +249,10 @@ class DDFPack(nn.Module):
         channel_filter = channel_filter.reshape(b * g, c // g, k, k).contiguous()
         if self.fuse_filter_norm and k >= 3:
             conv, norm = self.spatial_branch[0], self.spatial_branch[1]
-            raw = to_nchw(conv(x_in)).reshape(b * g, -1, h // s, w // s)
+            raw = spatial_raw_padded(conv, x_in)
+            if raw is None:
+                raw = to_nchw(conv(x_in))
+            raw = raw.reshape(b * g, -1, h // s, w // s)
             x = x.reshape(b * g, c // g, h, w)
             out = ddf_sfnorm(x, channel_filter, raw, self.kernel_size, self.dilation, self.stride,
                              self.kernel_combine, norm.std)

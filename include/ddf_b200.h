@@ -186,6 +186,12 @@ int ddf_b200_nhwc_to_nchw(const void* src, void* dst, int B, int C, int H, int W
                           void* stream);
 int ddf_b200_nchw_to_nhwc(const void* src, void* dst, int B, int C, int H, int W, int dtype,
                           const float* ch_scale, const float* ch_shift, int relu, void* stream);
+/* NHWC -> NCHW taking only the first C of src_channels >= C channels per pixel, with the same
+ * optional affine map and ReLU.  For the spatial branch: the library's 1x1 convolution is
+ * several times faster with its k*k = 9 output maps padded to 16, and its bias can ride here. */
+int ddf_b200_nhwc_to_nchw_affine(const void* src, void* dst, int B, int C, int H, int W,
+                                 int src_channels, int dtype, const float* ch_scale,
+                                 const float* ch_shift, int relu, void* stream);
 
 /*
  * Front end of a DDF layer in a channels-last network: ONE pass over x (B,H,W,C)

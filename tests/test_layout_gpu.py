@@ -42,6 +42,21 @@ def test_affine_relu_on_the_way(shape, dtype):
     assert torch.equal(got2, torch.relu(x))
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_nhwc_to_nchw_takes_leading_channels_and_adds_a_shift(dtype):
+    from ddfnet_b200.layout import to_nchw_affine
+    dev = torch.device("cuda:0")
+    for (B, SC, C, H, W) in ((2, 16, 9, 28, 28), (3, 32, 18, 7, 7), (1, 16, 16, 10, 6)):
+        x = torch.randn(B, SC, H, W, device=dev).to(dtype).contiguous(memory_format=torch.channels_last)
+        shift = torch.randn(C, device=dev)
+        ones = torch.ones(C, device=dev)
+        got = to_nchw_affine(x, C, ones, shift)
+        want = (x[:, :C].float() + shift.reshape(1, -1, 1, 1)).to(dtype)
+        assert got.is_contiguous() and got.shape == (B, C, H, W)
+        torch.testing.assert_close(got.float(), want.float(), rtol=2 ** -7 if dtype != torch.float32 else 1e-6,
+                                   atol=1e-6)
+
+
 def test_misaligned_pointer_is_refused():
     from ddfnet_b200 import _lib
     L = _lib.load()
