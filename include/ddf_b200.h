@@ -209,8 +209,9 @@ int ddf_b200_nhwc_to_nchw_affine(const void* src, void* dst, int B, int C, int H
  *                           n_partials = NT, pool_scale = 1/(H*W)
  * G = 0 skips the convolution (w_spatial, b_spatial, raw may then be NULL).  The
  * convolution runs on the CUDA cores (nine multiply-adds per element) and is slower
- * than the library's tensor-core convolution beyond C = 64: DDFPack uses G = 0 and
- * keeps the library convolution; see the design notes.
+ * than the library's tensor-core convolution (198 us against about 120 us per layer of
+ * ddf_mul_resnet50 at batch 256): the Python DDFPack calls this with G = 0 and keeps the
+ * library convolution.
  * The reference reads x once for each of these.  Inference path (no gradients);
  * dtype F32 / F16 / BF16; C <= 2048 and G*C*4 bytes <= 160 KB; x_nhwc and x_nchw
  * 16-byte aligned (DDF_B200_E_UNSUPPORTED otherwise).
