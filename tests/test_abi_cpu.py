@@ -65,6 +65,39 @@ def test_argument_checks(L):
     assert L.ddf_b200_backward_workspace(1, 4, 8, 8, 4, 1, 1, 0, 0, 0) == 0
 
 
+def test_argument_checks_of_the_adjacent_entry_points(L):
+    """Fused FilterNorm forward, layout adapters, front end, channel branch: every refusal
+    below happens before a device is touched (pointers are NULL or never dereferenced)."""
+    import ctypes
+    fake = ctypes.c_void_p(4096)   # non-NULL, 16-byte aligned, never dereferenced on these paths
+    # fused FilterNorm: k*k must exceed 1
+    assert L.ddf_b200_forward_sfnorm(fake, fake, fake, fake, 1, 4, 8, 8, 1, 1, 1, 0, 0, 0, 1.0, None) == -3
+    assert L.ddf_b200_forward_sfnorm(None, None, None, None, 1, 4, 8, 8, 3, 1, 1, 0, 0, 0, 1.0, None) == -1
+    # layout adapters
+    assert L.ddf_b200_nhwc_to_nchw(None, None, 1, 4, 8, 8, 0, None) == -1
+    assert L.ddf_b200_nhwc_to_nchw(fake, fake, 0, 4, 8, 8, 0, None) == -2
+    assert L.ddf_b200_nhwc_to_nchw(fake, fake, 1, 4, 8, 8, 3, None) == -5          # float64 not built
+    assert L.ddf_b200_nchw_to_nhwc(fake, fake, 1, 4, 8, 8, 0, fake, None, 0, None) == -1   # scale without shift
+    assert L.ddf_b200_nhwc_to_nchw_affine(fake, fake, 1, 9, 8, 8, 4, 0, None, None, 0, None) == -2  # source narrower
+    assert L.ddf_b200_nhwc_to_nchw(ctypes.c_void_p(4098), fake, 1, 4, 8, 8, 1, None) == -7  # misaligned
+    # front end
+    assert L.ddf_b200_frontend_tiles(56, 56) == 49 and L.ddf_b200_frontend_tiles(7, 7) == 1
+    assert L.ddf_b200_pack_frontend(None, None, None, None, None, None, 1, 4, 8, 8, 0, 1, 0, None) == -1
+    assert L.ddf_b200_pack_frontend(fake, fake, None, None, None, fake, 1, 4, 8, 8, 9, 1, 0, None) == -1
+    assert L.ddf_b200_pack_frontend(fake, fake, fake, fake, fake, fake, 1, 4, 8, 8, 40, 1, 0, None) == -7
+    assert L.ddf_b200_pack_frontend(fake, fake, None, None, None, fake, 1, 4, 8, 8, 0, 1, 3, None) == -5
+    # channel branch
+    cf = lambda *a: L.ddf_b200_channel_filter(fake, 1, 1.0, fake, fake, fake, fake, fake, fake, *a, None)
+    assert L.ddf_b200_channel_filter(None, 1, 1.0, fake, fake, fake, fake, fake, fake, 1, 64, 12, 3, 0, None) == -1
+    assert cf(0, 64, 12, 3, 0) == -2
+    assert cf(1, 64, 12, 7, 0) == -7       # k = 3 or 5 only
+    assert cf(1, 4096, 12, 3, 0) == -7     # C <= 2048
+    assert cf(1, 20, 4, 3, 0) == -7        # C a multiple of 8
+    assert cf(1, 300, 60, 3, 0) == -7      # above 256: a multiple of the 256-channel slice
+    assert cf(1, 64, 1000, 3, 0) == -7     # mid <= 512
+    assert L.ddf_b200_channel_filter_slice(64) == 64 and L.ddf_b200_channel_filter_slice(1024) == 256
+
+
 def test_plan_prefers_streaming_at_benchmark_shapes(L):
     from ddfnet_b200 import _lib
     for C, H, s in [(64, 56, 1), (128, 28, 1), (256, 14, 1), (512, 7, 1), (128, 56, 2), (256, 28, 2), (512, 14, 2)]:
