@@ -11,7 +11,7 @@ Inputs are seeded synthetic tensors: x ~ relu(N(0,1)), filters ~ N(0,1/9).
 
 Prints ONE JSON line.  `value` is algorithmic GB moved per second over the
 whole step with inputs resident in HBM, the step replayed from a CUDA graph and
-timed with CUDA events; `e2e` is the same sweep through `ddf_host` with pinned
+timed with CUDA events; `e2e` is the same sweep through `ddf_host_async` with pinned
 host buffers (host<->device copies inside the timed region); `roofline`
 describes the kernel instance that takes the largest share of the step;
 `cpu_baseline` is the CPU oracle (a port of the reference's arithmetic: the
@@ -185,7 +185,7 @@ def workload_config():
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     from ddfnet_b200 import _lib, ddf
-    from ddfnet_b200.host import ddf_host
+    from ddfnet_b200.host import ddf_host_async
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
@@ -282,15 +282,22 @@ def run_ours(args, rank, world, local_rank):
             for i, (C, H, s) in enumerate(SHAPES):
                 x, cf, sf = make_case(C, H, s, dtype, BATCH, None, 100 + i)
                 oh = H // s
+                # one output buffer per combine mode: the asynchronous calls of a step overlap
                 host_sets[(dtname, C, H, s)] = (x.pin_memory(), cf.pin_memory(), sf.pin_memory(),
-                                                torch.empty(BATCH, C, oh, oh, dtype=dtype, pin_memory=True))
+                                                {m: torch.empty(BATCH, C, oh, oh, dtype=dtype, pin_memory=True)
+                                                 for m in ("mul", "add")})
         h2d = sum(sum(t.numel() * t.element_size() for t in v[:3]) for v in host_sets.values()) * 2
-        d2h = sum(v[3].numel() * v[3].element_size() for v in host_sets.values()) * 2
+        d2h = sum(o.numel() * o.element_size() for v in host_sets.values() for o in v[3].values())
 
         def e2e_step():
+            # the 28 calls of a step are issued asynchronously (uploads, kernels and downloads
+            # of neighbouring calls overlap) and the step ends when every result is in host memory
+            pending = []
             for (mode, dtname, C, H, s, *_r) in cases:
                 hx, hcf, hsf, hout = host_sets[(dtname, C, H, s)]
-                ddf_host(hx, hcf, hsf, K, D, s, mode, out=hout, device=dev)
+                pending.append(ddf_host_async(hx, hcf, hsf, K, D, s, mode, out=hout[mode], device=dev))
+            for h_ in pending:
+                h_.wait()
 
         e2e_step()
         torch.cuda.synchronize()

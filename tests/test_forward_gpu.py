@@ -201,3 +201,21 @@ def test_runs_on_the_callers_stream():
         out = ddf(x, cf, sf, 3, 1, 1, "mul", "f")
     st.synchronize()
     check_close(out, want, torch.float16, "side stream")
+
+
+def test_host_buffers_sync_and_async_paths():
+    """ddf_host / ddf_host_async (pinned host tensors in, pinned host tensor out, chunks over
+    rotating streams) against the oracle; several asynchronous calls in flight at once."""
+    from ddfnet_b200.host import ddf_host, ddf_host_async
+    dtype = torch.bfloat16
+    cases = []
+    for i, (B, C, H, s) in enumerate([(64, 64, 56, 1), (32, 128, 28, 2), (48, 256, 14, 1)]):
+        x, cf, sf = make_inputs(B, C, H, H, 3, s, dtype, 900 + i, with_go=False)
+        cases.append((x.pin_memory(), cf.pin_memory(), sf.pin_memory(), s))
+    handles = [ddf_host_async(x, cf, sf, 3, 1, s, "mul", chunks=3) for (x, cf, sf, s) in cases]
+    for (x, cf, sf, s), h in zip(cases, handles):
+        out = h.wait()
+        assert out.is_pinned() and not out.is_cuda
+        check_close(out, oracle_forward(x, cf, sf, 3, 1, s, "mul"), dtype, "ddf_host_async")
+    x, cf, sf, s = cases[1]
+    check_close(ddf_host(x, cf, sf, 3, 1, s, "add"), oracle_forward(x, cf, sf, 3, 1, s, "add"), dtype, "ddf_host")
