@@ -127,8 +127,9 @@ def cpu_sweep_seconds(sample_batch, threads=None):
     """Times the float32 CPU oracle over the sweep's 7 shapes x 2 modes at a
     reduced batch.  Returns (seconds, 2-byte algorithmic bytes, threads used)."""
     from oracle import ddf_oracle
-    if threads:
-        ddf_oracle.set_threads(threads)
+    # All host cores unless told otherwise: torchrun exports OMP_NUM_THREADS=1 to its workers,
+    # which would otherwise leave the CPU arm on a single thread.
+    ddf_oracle.set_threads(threads or len(os.sched_getaffinity(0)))
     used = ddf_oracle.max_threads()
     total_s, total_b = 0.0, 0
     for i, (C, H, s) in enumerate(SHAPES):
