@@ -663,11 +663,15 @@ def run_model_reference(args, rank, world):
 
     name = args.model
     batch = 8
+    torch.set_num_threads(len(os.sched_getaffinity(0)))  # launchers may export OMP_NUM_THREADS=1
     orig = modules.ddf
     modules.ddf = lambda x, cf, sf, k, d, s, comb: ddf_oracle.composite_forward(x, cf, sf, k, d, s, comb)
     try:
         torch.manual_seed(0)
         model = MODELS[name]().eval()
+        for m in model.ddf_layers():   # the reference's module sequence, op by op
+            m.fuse_filter_norm = False
+            m.fuse_channel_branch = False
         x = torch.randn(batch, 3, 224, 224, generator=torch.Generator().manual_seed(1))
         with torch.no_grad():
             for _ in range(max(1, min(args.warmup, 1))):
