@@ -39,12 +39,9 @@ constexpr int kCbMaxC = 2048;
 constexpr int kCbMaxMid = 512;
 constexpr int kFaultChannelBranch = 5;
 
+// element -> float through the read-only path
 template <typename T>
-__device__ __forceinline__ float ldf(const T* p) { return (float)__ldg(p); }
-template <>
-__device__ __forceinline__ float ldf<__half>(const __half* p) { return __half2float(__ldg(p)); }
-template <>
-__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(__ldg(p)); }
+__device__ __forceinline__ float ldf(const T* p) { return (float)Elem<T>::load(p); }
 
 template <typename T>
 __device__ __forceinline__ float lds_elem(uint32_t a) {
