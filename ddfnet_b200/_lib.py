@@ -24,7 +24,7 @@ SYMBOLS = (
     "ddf_b200_launch_count", "ddf_b200_backward_noalloc", "ddf_b200_backward_noalloc_limit",
     "ddf_b200_forward_sfnorm", "ddf_b200_nhwc_to_nchw", "ddf_b200_nchw_to_nhwc", "ddf_b200_nhwc_to_nchw_affine",
     "ddf_b200_channel_filter", "ddf_b200_channel_filter_slice",
-    "ddf_b200_frontend_tiles", "ddf_b200_pack_frontend",
+    "ddf_b200_frontend_tiles", "ddf_b200_pack_frontend", "ddf_b200_forward_waitlimit",
 )
 
 
@@ -51,6 +51,8 @@ def load() -> ctypes.CDLL:
         L.ddf_b200_strerror.argtypes = [i]
         L.ddf_b200_forward.restype = i
         L.ddf_b200_forward.argtypes = [vp] * 4 + [i] * 10 + [vp]
+        L.ddf_b200_forward_waitlimit.restype = i
+        L.ddf_b200_forward_waitlimit.argtypes = [vp] * 4 + [i] * 9 + [ctypes.c_longlong, i, vp]
         L.ddf_b200_forward_sfnorm.restype = i
         L.ddf_b200_forward_sfnorm.argtypes = [vp] * 4 + [i] * 10 + [ctypes.c_double, vp]
         L.ddf_b200_nhwc_to_nchw.restype = i

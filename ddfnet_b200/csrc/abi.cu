@@ -6,6 +6,7 @@
 #include "bwd_stream.cuh"
 #include "common.cuh"
 #include "generic.cuh"
+#include "ring_fwd.cuh"
 #include "stream_fwd.cuh"
 
 #include <cstdlib>
@@ -15,25 +16,25 @@ namespace ddf {
 __device__ int g_fault_word = 0;
 
 std::atomic<unsigned long long> g_launches{0};  // also counted from layout.cu
-
 struct DeviceInfo {
     int sm_count = 0;
     int cc_major = 0;
     int* fault = nullptr;
     int index = 0;
-    bool ready = false;
+    std::atomic<bool> ready{false};
 };
 static DeviceInfo g_dev[64];
 
-// Per-device facts, fetched once per device (benign if two threads race: both
-// write the same values).
+// Per-device facts, fetched once per device.  Two threads may both fill the entry (with
+// the same values); `ready` is published with release / read with acquire so that a thread
+// that sees it set also sees the fields.
 static int device_info(DeviceInfo*& out) {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= 64) return DDF_B200_E_DEVICE;
     DeviceInfo& di = g_dev[dev];
-    if (!di.ready) {
+    if (!di.ready.load(std::memory_order_acquire)) {
         int sm = 0, major = 0;
         e = cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev);
         if (e != cudaSuccess) return (int)e;
@@ -46,7 +47,7 @@ static int device_info(DeviceInfo*& out) {
         di.cc_major = major;
         di.fault = reinterpret_cast<int*>(fp);
         di.index = dev;
-        di.ready = true;
+        di.ready.store(true, std::memory_order_release);
     }
     if (di.cc_major != 10) return DDF_B200_E_DEVICE;
     out = &di;
@@ -215,33 +216,25 @@ static int stream_pixels(const Problem& p, bool bwdx) {
     return 0;
 }
 
-// Planes per thread per pass the streaming kernels try first.  DDF_B200_PPT=1 in the
-// environment restores one plane per thread (A/B timing).
-static int stream_ppt() {
-    static const int v = [] {
-        const char* e = std::getenv("DDF_B200_PPT");
-        return (e && e[0] == '1' && e[1] == 0) ? 1 : 2;
-    }();
-    return v;
-}
-
-// Target size of one ring stage: 0 lets the planner choose by plane size;
-// DDF_B200_STAGE_KB=4..96 in the environment fixes it (A/B timing).
-static int stream_stage_bytes() {
-    static const int v = [] {
-        const char* e = std::getenv("DDF_B200_STAGE_KB");
-        const int kb = e ? std::atoi(e) : 0;
-        return (kb >= 4 && kb <= 96 ? kb : 0) * 1024;
-    }();
-    return v;
-}
-
 static int run_stream(const StreamArgs& a, cudaStream_t st) {
     int rc;
     switch (a.p.dtype) {
         case DDF_B200_F32: rc = stream_dispatch<float>(a, st); break;
         case DDF_B200_F16: rc = stream_dispatch<__half>(a, st); break;
         case DDF_B200_BF16: rc = stream_dispatch<__nv_bfloat16>(a, st); break;
+        default: rc = kNotHandled;
+    }
+    if (rc == 0) g_launches.fetch_add(1, std::memory_order_relaxed);
+    return rc;
+}
+
+// Plane-ring kernels (2-byte element types).  Returns kNotHandled when no instantiation
+// covers the problem.
+static int run_ring(const RingArgs& a, cudaStream_t st) {
+    int rc;
+    switch (a.p.dtype) {
+        case DDF_B200_F16: rc = ring_dispatch<__half>(a, st); break;
+        case DDF_B200_BF16: rc = ring_dispatch<__nv_bfloat16>(a, st); break;
         default: rc = kNotHandled;
     }
     if (rc == 0) g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -267,9 +260,14 @@ static int forward_impl(const Problem& p, const void* x, const void* cf, const v
     if (variant != DDF_B200_VARIANT_GENERIC) {
         const int P = stream_pixels(p, false);
         const bool want = variant == DDF_B200_VARIANT_STREAM || stream_worthwhile(p, di->sm_count);
+        if (want) {
+            RingArgs ra{x, cf, sf, out, p, false, di->sm_count, di->fault, di->index,
+                        true, 0, 0u};
+            rc = run_ring(ra, st);
+            if (rc != kNotHandled) return rc;
+        }
         if (P > 0 && want) {
-            StreamArgs a{x, cf, sf, out, p, false, di->sm_count, di->fault, P, di->index, stream_ppt(),
-                         stream_stage_bytes(), overlap_launch_enabled() && p.k == 3};
+            StreamArgs a{x, cf, sf, out, p, false, di->sm_count, di->fault, P, di->index, 2, 0, p.k == 3};
             rc = run_stream(a, st);
             if (rc != kNotHandled) return rc;
         }
@@ -349,6 +347,23 @@ int ddf_b200_forward(const void* x, const void* cf, const void* sf, void* out, i
     return forward_impl(p, x, cf, sf, out, variant, stream);
 }
 
+int ddf_b200_forward_waitlimit(const void* x, const void* cf, const void* sf, void* out, int B, int C,
+                               int H, int W, int k, int d, int s, int combine, int dtype,
+                               long long wait_cycles, int starve, void* stream) {
+    Problem p;
+    int rc = check_problem(B, C, H, W, k, d, s, combine, dtype, DDF_B200_VARIANT_STREAM, p);
+    if (rc) return rc;
+    if (!x || !cf || !sf || !out) return DDF_B200_E_NULL;
+    if (wait_cycles < 1) return DDF_B200_E_SHAPE;
+    DeviceInfo* di = nullptr;
+    rc = device_info(di);
+    if (rc) return rc;
+    RingArgs ra{x, cf, sf, out, p, false, di->sm_count, di->fault, di->index, false, wait_cycles,
+                starve ? 16u : 0u};
+    rc = run_ring(ra, reinterpret_cast<cudaStream_t>(stream));
+    return rc == kNotHandled ? DDF_B200_E_UNSUPPORTED : rc;
+}
+
 int ddf_b200_forward_sfnorm(const void* x, const void* cf, const void* sf_raw, void* out, int B,
                             int C, int H, int W, int k, int d, int s, int combine, int dtype,
                             int variant, double sf_scale, void* stream) {
@@ -389,13 +404,26 @@ int ddf_b200_backward(const void* go, const void* x, const void* cf, const void*
     const bool allow_stream = variant != DDF_B200_VARIANT_GENERIC;
     const bool want = variant == DDF_B200_VARIANT_STREAM || stream_worthwhile(p, di->sm_count);
 
+    // Decide the filter-gradient path first, so that a missing workspace is reported before
+    // anything has been launched.  Only the spatial-filter gradient uses the workspace.
+    const bool filters_stream = (gcf || gsf) && allow_stream && want && bwd_stream_supported(p);
+    if (filters_stream && gsf) {
+        const size_t need = bwd_stream_workspace(p, di->sm_count);
+        if (need > 0 && (!workspace || workspace_bytes < need)) return DDF_B200_E_WORKSPACE;
+    }
+
     // grad wrt x: the streaming forward kernel run over go with mirrored taps.
     if (gx) {
         bool done = false;
         if (allow_stream && want) {
-            const int P = stream_pixels(p, true);
+            RingArgs ra{go, cf, sf, gx, p, true, di->sm_count, di->fault, di->index,
+                        true, 0, 0u};
+            rc = run_ring(ra, st);
+            if (rc == 0) done = true;
+            else if (rc != kNotHandled) return rc;
+            const int P = done ? 0 : stream_pixels(p, true);
             if (P > 0) {
-                StreamArgs a{go, cf, sf, gx, p, true, di->sm_count, di->fault, P, di->index, stream_ppt(), stream_stage_bytes(), overlap_launch_enabled() && p.k == 3};
+                StreamArgs a{go, cf, sf, gx, p, true, di->sm_count, di->fault, P, di->index, 2, 0, p.k == 3};
                 rc = run_stream(a, st);
                 if (rc == 0) done = true;
                 else if (rc != kNotHandled) return rc;
@@ -411,11 +439,9 @@ int ddf_b200_backward(const void* go, const void* x, const void* cf, const void*
     // grads wrt the two filters.
     if (gcf || gsf) {
         bool done = false;
-        if (allow_stream && want && bwd_stream_supported(p)) {
-            const size_t need = bwd_stream_workspace(p, di->sm_count);
-            if (need > 0 && (!workspace || workspace_bytes < need)) return DDF_B200_E_WORKSPACE;
+        if (filters_stream) {
             int launches = 0;
-            rc = bwd_stream_filters(p, go, x, cf, sf, gcf, gsf, workspace, di->sm_count, di->fault,
+            rc = bwd_stream_filters(p, go, x, cf, sf, gcf, gsf, gsf ? workspace : nullptr, di->sm_count, di->fault,
                                     di->index, st, &launches);
             if (rc == 0) {
                 done = true;

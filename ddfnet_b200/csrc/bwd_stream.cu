@@ -1,4 +1,6 @@
 // Streaming filter-gradient kernels: host-side entry (see bwd_stream.cuh).
+#include <atomic>
+
 #include "bwd_stream.cuh"
 
 #include "bwd_stream_impl.cuh"
@@ -47,7 +49,7 @@ int bwd_stream_filters(const Problem& p, const void* go, const void* x, const vo
     BwdGeometry g;
     const int P = bwd_pixels(p, sm_count, g);
     if (P == 0) return kNotHandled;
-    BwdArgs a{go, x, cf, sf, gcf, gsf, workspace, p, sm_count, fault, P, device, overlap_launch_enabled() && p.k == 3};
+    BwdArgs a{go, x, cf, sf, gcf, gsf, workspace, p, sm_count, fault, P, device, p.k == 3};
     switch (p.dtype) {
         case DDF_B200_F32: return bwd_dispatch<float>(a, st, launches);
         case DDF_B200_F16: return bwd_dispatch<__half>(a, st, launches);
@@ -81,18 +83,18 @@ namespace ddf {
 constexpr size_t kStaticScratchBytes = 16u << 20;  // 16 MiB per GPU
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-static void* g_static_scratch_ptr[64] = {nullptr};
+static std::atomic<void*> g_static_scratch_ptr[64];
 
 // Device address of the static scratch on the current device (set up on first use).
 static int static_scratch_address(int device, void** out) {
     if (device < 0 || device >= 64) return DDF_B200_E_DEVICE;
-    if (g_static_scratch_ptr[device] == nullptr) {
-        void* ptr = nullptr;
+    void* ptr = g_static_scratch_ptr[device].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
         const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
         if (e != cudaSuccess) return (int)e;
-        g_static_scratch_ptr[device] = ptr;
+        g_static_scratch_ptr[device].store(ptr, std::memory_order_release);
     }
-    *out = g_static_scratch_ptr[device];
+    *out = ptr;
     return 0;
 }
 
@@ -120,10 +122,12 @@ int ddf_b200_backward_noalloc(const void* go, const void* x, const void* cf, con
     rc = device_facts(&sm_count, &fault, &index);
     if (rc) return rc;
 
-    // Refuse before anything is launched if the filter gradients would need more
-    // scratch than the built-in array holds.
-    const bool streaming = (gcf || gsf) && bwd_stream_supported(p);
-    if (streaming && bwd_stream_workspace(p, sm_count) > kStaticScratchBytes)
+    // The same kernel choice as ddf_b200_backward makes under AUTO, so that both entry
+    // points give bit-identical results.  Only the spatial-filter gradient uses scratch:
+    // refuse, before anything is launched, if it would need more than the array holds.
+    const bool streaming = (gcf || gsf) &&
+                           ddf_b200_plan(B, C, H, W, k, d, s, combine, dtype, 1) == DDF_B200_VARIANT_STREAM;
+    if (streaming && gsf && bwd_stream_workspace(p, sm_count) > kStaticScratchBytes)
         return DDF_B200_E_SCRATCH_LIMIT;
 
     // grad-x needs no scratch: regular entry point, filter gradients not requested.
@@ -136,8 +140,10 @@ int ddf_b200_backward_noalloc(const void* go, const void* x, const void* cf, con
 
     if (streaming) {
         void* scratch = nullptr;
-        rc = static_scratch_address(index, &scratch);
-        if (rc) return rc;
+        if (gsf) {
+            rc = static_scratch_address(index, &scratch);
+            if (rc) return rc;
+        }
         int launches = 0;
         rc = bwd_stream_filters(p, go, x, cf, sf, gcf, gsf, scratch, sm_count, fault, index,
                                 reinterpret_cast<cudaStream_t>(stream), &launches);

@@ -53,6 +53,7 @@ struct BwdPlan {
     int warps_per_plane;
     long long total_passes;
     uint32_t xplane_bytes, gplane_bytes, sf_bytes;
+    unsigned long long x_total, go_total, cf_total, sf_total;   // byte sizes of the whole tensors
     uint32_t off_zero, off_cfc, cfc_stride, off_sf, off_stage0, stage_stride;
     uint32_t off_x, off_rawcf, off_gpart;  // inside a stage
     int* fault;
@@ -174,11 +175,9 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
                     (seg_k == 0 || warp_test(bar_sf_empty, (uint32_t)((seg_k - 1) & 1), lane))) {
                     if (lane == 0) {
                         const unsigned long long g0 = (unsigned long long)seg_b * pl.sf_bytes;
-                        const unsigned long long a0 = g0 & ~15ull;
-                        const unsigned long long a1 = (g0 + pl.sf_bytes + 15ull) & ~15ull;
-                        mbar_arrive_expect_tx(bar_sf_full, (uint32_t)(a1 - a0));
-                        bulk_g2s(sbase + pl.off_sf, (const char*)pl.sf + a0, (uint32_t)(a1 - a0),
-                                 bar_sf_full);
+                        const Span sp = span_prepare(sbase + pl.off_sf, pl.sf, g0, g0 + pl.sf_bytes, pl.sf_total);
+                        mbar_arrive_expect_tx(bar_sf_full, sp.bytes);
+                        span_issue(sp, bar_sf_full);
                     }
                     ++seg_k;
                     ++seg_b;
@@ -196,22 +195,19 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
                 if (st_end > plane_hi) st_end = plane_hi;
                 if (lane == 0) {
                     const unsigned long long n0 = (unsigned long long)st_first, n1 = (unsigned long long)st_end;
-                    const unsigned long long x0 = (n0 * pl.xplane_bytes) & ~15ull;
-                    const unsigned long long x1 = (n1 * pl.xplane_bytes + 15ull) & ~15ull;
-                    const unsigned long long g0 = (n0 * pl.gplane_bytes) & ~15ull;
-                    const unsigned long long g1 = (n1 * pl.gplane_bytes + 15ull) & ~15ull;
-                    const unsigned long long c0 = (n0 * (KK * ES)) & ~15ull;
-                    const unsigned long long c1 = (n1 * (KK * ES) + 15ull) & ~15ull;
-                    uint32_t bytes = (uint32_t)((x1 - x0) + (g1 - g0));
-                    if constexpr (MUL) bytes += (uint32_t)(c1 - c0);
-                    mbar_arrive_expect_tx(BAR_FULL(slot), bytes);
-                    bulk_g2s(STAGE_BASE(slot) + 32u, (const char*)pl.go + g0, (uint32_t)(g1 - g0),
-                             BAR_FULL(slot));
-                    bulk_g2s(STAGE_BASE(slot) + pl.off_x, (const char*)pl.x + x0, (uint32_t)(x1 - x0),
-                             BAR_FULL(slot));
+                    // a copy never reads past its tensor's last whole 16 bytes (see span_prepare)
+                    const Span sg = span_prepare(STAGE_BASE(slot) + 32u, pl.go, n0 * pl.gplane_bytes,
+                                                 n1 * pl.gplane_bytes, pl.go_total);
+                    const Span sx = span_prepare(STAGE_BASE(slot) + pl.off_x, pl.x, n0 * pl.xplane_bytes,
+                                                 n1 * pl.xplane_bytes, pl.x_total);
+                    Span sc{0u, nullptr, 0u};
                     if constexpr (MUL)
-                        bulk_g2s(STAGE_BASE(slot) + pl.off_rawcf, (const char*)pl.cf + c0,
-                                 (uint32_t)(c1 - c0), BAR_FULL(slot));
+                        sc = span_prepare(STAGE_BASE(slot) + pl.off_rawcf, pl.cf, n0 * (KK * ES), n1 * (KK * ES),
+                                          pl.cf_total);
+                    mbar_arrive_expect_tx(BAR_FULL(slot), sg.bytes + sx.bytes + sc.bytes);
+                    span_issue(sg, BAR_FULL(slot));
+                    span_issue(sx, BAR_FULL(slot));
+                    span_issue(sc, BAR_FULL(slot));
                 }
                 ++issue_i;
                 progress = true;
@@ -643,9 +639,6 @@ bool make_bwd_plan(const BwdArgs& a, BwdPlan& pl, uint32_t& smem_bytes, BwdGeome
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
     if (!al16(a.go) || !al16(a.x) || !al16(a.cf) || !al16(a.sf)) return false;
     if (a.workspace && !al16(a.workspace)) return false;
-    if ((planes * xpb) % 16 != 0 || (planes * gpb) % 16 != 0) return false;
-    if ((planes * G::KK * G::ES) % 16 != 0) return false;
-    if (((long long)p.B * sfb) % 16 != 0) return false;
 
     // Stages of about 48 KB: the service warp's per-stage duties (expanding channel
     // filters, folding the grad-cf partials, three copies) are a serial chain; with
@@ -696,6 +689,10 @@ bool make_bwd_plan(const BwdArgs& a, BwdPlan& pl, uint32_t& smem_bytes, BwdGeome
     pl.xplane_bytes = xpb;
     pl.gplane_bytes = gpb;
     pl.sf_bytes = sfb;
+    pl.x_total = (unsigned long long)planes * xpb;
+    pl.go_total = (unsigned long long)planes * gpb;
+    pl.cf_total = (unsigned long long)planes * G::KK * G::ES;
+    pl.sf_total = (unsigned long long)p.B * sfb;
     pl.fault = a.fault;
     return true;
 }

@@ -164,6 +164,35 @@ __device__ __forceinline__ void sts32(uint32_t a, uint32_t v) {
     asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
 }
 
+__device__ __forceinline__ void sts16(uint32_t a, uint32_t v) {
+    asm volatile("st.shared.u16 [%0], %1;" ::"r"(a), "h"((uint16_t)v) : "memory");
+}
+
+// Copy-issuer helper: bytes [g0, g1) of a tensor (16-byte aligned base, `total` bytes) go to
+// shared memory such that byte g lands at dst + (g - (g0 & ~15)).  The aligned superset is
+// fetched by one bulk copy, clamped to the tensor's last whole 16 bytes; what is left of a
+// ragged end is fetched with plain 2-byte loads.  span_prepare does the plain part and
+// returns the bulk part; call it before mbarrier.arrive.expect_tx, span_issue after.
+struct Span { uint32_t dst; const char* src; uint32_t bytes; };
+__device__ __forceinline__ Span span_prepare(uint32_t dst, const void* base, unsigned long long g0,
+                                             unsigned long long g1, unsigned long long total) {
+    const unsigned long long a0 = g0 & ~15ull;
+    unsigned long long a1 = (g1 + 15ull) & ~15ull;
+    const unsigned long long lim = total & ~15ull;
+    if (a1 > lim) a1 = lim;
+    if (a1 < a0) a1 = a0;
+    const char* b = reinterpret_cast<const char*>(base);
+    for (unsigned long long g = (a1 > g0 ? a1 : g0); g < g1; g += 2) {
+        uint16_t v;
+        asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(b + g));
+        sts16(dst + (uint32_t)(g - a0), v);
+    }
+    return Span{dst, b + a0, (uint32_t)(a1 - a0)};
+}
+__device__ __forceinline__ void span_issue(const Span& s, uint32_t bar) {
+    if (s.bytes) bulk_g2s(s.dst, s.src, s.bytes, bar);
+}
+
 // ------------------------------------------------------------------ packed f32x2
 __device__ __forceinline__ unsigned long long f2_pack(float a, float b) {
     unsigned long long r;

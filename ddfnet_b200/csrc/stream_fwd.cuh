@@ -26,9 +26,10 @@
 //
 // Bulk copies must start on 16-byte boundaries.  Plane runs start anywhere, so
 // every copy fetches the 16-byte-aligned superset of the bytes it needs and the
-// readers add the remainder (< 16 bytes) to their shared-memory addresses; the
-// launcher declines (kNotHandled) when a tensor's base or total size is not a
-// multiple of 16 bytes, and the caller then uses the generic kernel.
+// readers add the remainder (< 16 bytes) to their shared-memory addresses.  A copy
+// never reads past the tensor's last whole 16 bytes: what is left of a ragged end
+// is fetched with plain loads.  The launcher declines (kNotHandled) only when a
+// tensor's base address is not 16-byte aligned.
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records a fault
 // code in global memory and the thread leaves the kernel.
@@ -64,6 +65,7 @@ struct StreamPlan {
     long long total_passes;  // B*C / NP
     uint32_t plane_bytes;    // H*W*sizeof(T)
     uint32_t sf_bytes;       // k*k*OH*OW*sizeof(T): one sample's spatial filter
+    unsigned long long in_total, cf_total, sf_total;   // byte sizes of the whole tensors
     uint32_t off_zero, off_cfc, cfc_stride, off_sf, off_stage0, stage_stride, off_rawcf;
     int* fault;
     float sf_scale;  // NORM kernels: output scale of the spatial FilterNorm (gain / k)
@@ -313,11 +315,9 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                     (seg_k == 0 || warp_test(bar_sf_empty, (uint32_t)((seg_k - 1) & 1), lane))) {
                     if (lane == 0) {
                         const unsigned long long g0 = (unsigned long long)seg_b * pl.sf_bytes;
-                        const unsigned long long a0 = g0 & ~15ull;
-                        const unsigned long long a1 = (g0 + pl.sf_bytes + 15ull) & ~15ull;
-                        mbar_arrive_expect_tx(bar_sf_full, (uint32_t)(a1 - a0));
-                        bulk_g2s(sbase + pl.off_sf, (const char*)pl.sf + a0, (uint32_t)(a1 - a0),
-                                 bar_sf_full);
+                        const Span sp = span_prepare(sbase + pl.off_sf, pl.sf, g0, g0 + pl.sf_bytes, pl.sf_total);
+                        mbar_arrive_expect_tx(bar_sf_full, sp.bytes);
+                        span_issue(sp, bar_sf_full);
                     }
                     ++seg_k;
                     ++seg_b;
@@ -338,15 +338,13 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                     if (lane == 0) {
                         const unsigned long long g0 = (unsigned long long)st_first * pl.plane_bytes;
                         const unsigned long long g1 = (unsigned long long)st_end * pl.plane_bytes;
-                        const unsigned long long a0 = g0 & ~15ull, a1 = (g1 + 15ull) & ~15ull;
                         const unsigned long long c0 = (unsigned long long)st_first * (KK * ES);
                         const unsigned long long c1 = (unsigned long long)st_end * (KK * ES);
-                        const unsigned long long ca0 = c0 & ~15ull, ca1 = (c1 + 15ull) & ~15ull;
-                        mbar_arrive_expect_tx(BAR_FULL(slot), (uint32_t)((a1 - a0) + (ca1 - ca0)));
-                        bulk_g2s(STAGE_BASE(slot) + 32u, (const char*)pl.in + a0,
-                                 (uint32_t)(a1 - a0), BAR_FULL(slot));
-                        bulk_g2s(STAGE_BASE(slot) + pl.off_rawcf, (const char*)pl.cf + ca0,
-                                 (uint32_t)(ca1 - ca0), BAR_FULL(slot));
+                        const Span sx = span_prepare(STAGE_BASE(slot) + 32u, pl.in, g0, g1, pl.in_total);
+                        const Span sc = span_prepare(STAGE_BASE(slot) + pl.off_rawcf, pl.cf, c0, c1, pl.cf_total);
+                        mbar_arrive_expect_tx(BAR_FULL(slot), sx.bytes + sc.bytes);
+                        span_issue(sx, BAR_FULL(slot));
+                        span_issue(sc, BAR_FULL(slot));
                     }
                     ++issue_i;
                     progress = true;
@@ -690,16 +688,6 @@ cudaError_t launch_overlapped(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
-// Programmatic dependent launch is on unless DDF_B200_PDL=0 is set in the environment.
-// Callers use it for k = 3 only: the k = 5 'mul' backward measured 3-8 % slower with it.
-inline bool overlap_launch_enabled() {
-    static const bool v = [] {
-        const char* e = std::getenv("DDF_B200_PDL");
-        return !(e && e[0] == '0');
-    }();
-    return v;
-}
-
 struct StreamArgs {
     const void* in;
     const void* cf;
@@ -743,9 +731,6 @@ bool make_stream_plan(const StreamArgs& a, StreamPlan& pl, uint32_t& smem_bytes,
     // 16-byte rules of the bulk copies.
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
     if (!al16(a.in) || !al16(a.cf) || !al16(a.sf) || !al16(a.out)) return false;
-    if ((planes * plane_bytes) % 16 != 0) return false;
-    if ((planes * G::KK * G::ES) % 16 != 0) return false;
-    if (((long long)p.B * sf_bytes) % 16 != 0) return false;
 
     // Stage size.  The service warp does a fixed amount of serial work per stage, so
     // large planes (>= 3 KB) want stages of two or more passes and about 48 KB;
@@ -799,6 +784,9 @@ bool make_stream_plan(const StreamArgs& a, StreamPlan& pl, uint32_t& smem_bytes,
     pl.total_passes = total_passes;
     pl.plane_bytes = plane_bytes;
     pl.sf_bytes = sf_bytes;
+    pl.in_total = (unsigned long long)planes * plane_bytes;
+    pl.cf_total = (unsigned long long)planes * G::KK * G::ES;
+    pl.sf_total = (unsigned long long)p.B * sf_bytes;
     pl.fault = a.fault;
     if (a.bwdx && p.sf_norm) return false;  // grad-x takes the normalised filter
     pl.sf_scale = (float)p.sf_scale;
@@ -806,21 +794,13 @@ bool make_stream_plan(const StreamArgs& a, StreamPlan& pl, uint32_t& smem_bytes,
     return true;
 }
 
-#ifndef DDF_PACK_F32X2
-#define DDF_PACK_F32X2 1
-#endif
-#ifndef DDF_PACK_ODD
-#define DDF_PACK_ODD 1
-#endif
-
 template <typename T, int K, int D, int S, int P, int MODE, bool BWDX, int PPT = 1, bool NORM = false>
 int stream_launch(const StreamArgs& a, cudaStream_t stream) {
     StreamPlan pl;
     uint32_t smem = 0;
     int grid = 0;
     if (!make_stream_plan<T, K, D, S, P, PPT>(a, pl, smem, grid)) return kNotHandled;
-    constexpr bool PACK = (DDF_PACK_F32X2 != 0) && sizeof(T) == 2 && P >= 2 &&
-                          (P % 2 == 0 || (DDF_PACK_ODD != 0 && PPT == 1));
+    constexpr bool PACK = sizeof(T) == 2 && P >= 2 && (P % 2 == 0 || PPT == 1);
     if (NORM != (a.p.sf_norm != 0)) return kNotHandled;
     auto kern = stream_kernel<T, K, D, S, P, MODE, BWDX, PACK, PPT, NORM>;
     // Opt in to the large dynamic shared-memory carve-out once per device and

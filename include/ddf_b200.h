@@ -101,6 +101,23 @@ int ddf_b200_forward_sfnorm(const void* x, const void* cf, const void* sf_raw, v
                             int B, int C, int H, int W, int k, int d, int s,
                             int combine, int dtype, int variant, double sf_scale, void* stream);
 
+/*
+ * Self-test of the bounded waits.  Runs the plane-ring forward kernel (2-byte element
+ * types at the row widths it is built for; DDF_B200_E_UNSUPPORTED otherwise) with every
+ * mbarrier wait limited to `wait_cycles` SM clocks.  With `starve` != 0 each stage is
+ * announced 16 bytes larger than what is copied, so its barrier never completes: the
+ * compute warps' waits run out, the kernel records fault 1 (a compute warp gave up
+ * waiting for a stage) and returns with `out` partly unwritten, and the device context
+ * stays usable.  ddf_b200_take_fault() then returns 1.  With `starve` == 0 the call is an
+ * ordinary forward with a custom limit.  Replaces the reference's error convention for
+ * this path -- print and exit(-1) on a failed launch
+ * (ddf/src/cuda/ddf_mul_cuda_kernel.cu:190-194) -- with a status the host can read.
+ */
+int ddf_b200_forward_waitlimit(const void* x, const void* cf, const void* sf, void* out,
+                               int B, int C, int H, int W, int k, int d, int s,
+                               int combine, int dtype, long long wait_cycles, int starve,
+                               void* stream);
+
 /* Which variant (GENERIC or STREAM) AUTO resolves to for this problem; pointers
  * are assumed 16-byte aligned.  `backward` = 0 for the forward, 1 for the backward.
  * Returns a DDF_B200_VARIANT_* value, or a negative status. */

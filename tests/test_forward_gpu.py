@@ -45,9 +45,6 @@ def test_generic_forward(shape, dt):
 
 
 # ------------------------------------------------------------------ streaming kernel
-# (The streaming kernels take a tensor only if its byte size is a multiple of 16:
-# the batch sizes below are chosen accordingly; other sizes fall back to the
-# generic kernel, which test_auto_falls_back covers.)
 # B, C, H, W, k, d, s -- every (k, d, s, P) instantiation, plane runs that cross
 # sample boundaries inside a CTA, several samples inside one stage (small C),
 # fewer plane groups than SMs, and widths for each pixels-per-thread choice.
@@ -71,6 +68,11 @@ STREAM = [
     (2, 24, 20, 24, 3, 1, 1),    # non-square, H*W/8 = 60 tasks, 6 planes per pass
     (1, 8, 40, 64, 3, 1, 1),     # wide plane, single sample
     (2, 16, 16, 8, 3, 1, 1),
+    (2, 64, 56, 56, 3, 1, 1),    # plane-ring kernel (2-byte types): one plane per pass
+    (5, 24, 28, 28, 3, 1, 1),    # plane-ring: three planes per pass, run crossing samples
+    (3, 48, 14, 14, 3, 1, 1),    # plane-ring: sixteen planes per pass
+    (5, 40, 28, 28, 3, 1, 2),    # plane-ring, stride 2
+    (2, 8, 57, 56, 3, 1, 1),     # 56 wide but 57 high: ring kernel with a non-square plane
 ]
 
 
@@ -86,16 +88,62 @@ def test_stream_forward(shape, dt):
     _no_fault()
 
 
-def test_auto_falls_back():
-    """Sizes the streaming kernels decline (a tensor whose byte size is not a
-    multiple of 16, here sf) are served by the generic kernel under AUTO and refused
-    under 'f'."""
-    from ddfnet_b200._lib import DDFError
-    x, cf, sf = make_inputs(5, 32, 14, 14, 3, 1, torch.bfloat16, seed=3, with_go=False)
-    with pytest.raises(DDFError):
-        _run(x, cf, sf, 3, 1, 1, "mul", "f")
-    check_close(_run(x, cf, sf, 3, 1, 1, "mul", ""), oracle_forward(x, cf, sf, 3, 1, 1, "mul"),
-                torch.bfloat16, "auto fallback")
+RAGGED = [(5, 32, 14, 14), (12, 32, 14, 14), (5, 64, 7, 7), (12, 64, 7, 7), (3, 24, 14, 14), (7, 8, 7, 7)]
+
+
+@pytest.mark.parametrize("shape", RAGGED)
+@pytest.mark.parametrize("dt", ["bf16", "f16", "f32"])
+def test_streaming_kernels_take_ragged_sizes(shape, dt):
+    """Batch sizes whose tensors are not multiples of 16 bytes (every B that is not a multiple
+    of 8 at 7x7, every odd B at 14x14 in the 2-byte types): the bulk copies stop at the
+    tensor's last whole 16 bytes and the rest is fetched with plain loads, so the streaming
+    kernels serve them ('f') -- also when the tensors sit at the very end of an allocation."""
+    B, C, H, W = shape
+    dtype = DTYPES[dt]
+    dev = torch.device("cuda:0")
+    x, cf, sf = make_inputs(B, C, H, W, 3, 1, dtype, seed=300 + B + H, with_go=False)
+
+    def at_end(t):   # a view that ends exactly at the end of its own allocation
+        flat = torch.empty(t.numel() + 128, dtype=t.dtype, device=dev)
+        v = flat[128:].view(t.shape)
+        v.copy_(t)
+        return v
+
+    from ddfnet_b200 import ddf
+    for m in ("mul", "add"):
+        out = ddf(at_end(x), at_end(cf), at_end(sf), 3, 1, 1, m, "f")
+        check_close(out, oracle_forward(x, cf, sf, 3, 1, 1, m), dtype, f"ragged {shape} {dt} {m}")
+    _no_fault()
+
+
+def test_wait_limit_reports_a_fault_and_the_context_survives():
+    """A bounded wait that runs out: every stage is announced 16 bytes larger than what is
+    copied, so no stage ever completes; with a limit of about a millisecond the compute warps
+    give up, the kernel returns, the fault word reads 1 (a compute warp gave up waiting for a
+    stage) and the next ordinary call works."""
+    lib = _lib()
+    L = lib.load()
+    dev = torch.device("cuda:0")
+    B, C, H = 8, 64, 28
+    x, cf, sf = (t.to(dev) for t in make_inputs(B, C, H, H, 3, 1, torch.bfloat16, 77, with_go=False))
+    out = torch.empty_like(x)
+    stream = torch.cuda.current_stream().cuda_stream
+    args = (x.data_ptr(), cf.data_ptr(), sf.data_ptr(), out.data_ptr(), B, C, H, H, 3, 1, 1, lib.MUL, lib.BF16)
+    assert L.ddf_b200_take_fault() == 0
+    assert L.ddf_b200_forward_waitlimit(*args, 2_000_000, 1, stream) == 0
+    assert L.ddf_b200_take_fault() == 1
+    assert L.ddf_b200_take_fault() == 0          # reading the word clears it
+    # the same entry point without starvation is an ordinary forward
+    assert L.ddf_b200_forward_waitlimit(*args, 2_000_000_000, 0, stream) == 0
+    want = oracle_forward(x.cpu(), cf.cpu(), sf.cpu(), 3, 1, 1, "mul")
+    check_close(out, want, torch.bfloat16, "after a starved launch")
+    check_close(_run(x, cf, sf, 3, 1, 1, "mul"), want, torch.bfloat16, "ordinary call after a starved launch")
+    _no_fault()
+    # shapes outside the ring kernel's set are refused, not run
+    xf = x.float()
+    assert L.ddf_b200_forward_waitlimit(xf.data_ptr(), cf.float().data_ptr(), sf.float().data_ptr(),
+                                        torch.empty_like(xf).data_ptr(), B, C, H, H, 3, 1, 1, lib.MUL, lib.F32,
+                                        2_000_000, 0, stream) == -7
 
 
 def test_stream_rejects_what_it_cannot_do():

@@ -66,6 +66,40 @@ def test_noalloc_backward_matches_regular_entry_point(dt, dtc, mode, comb):
     assert L.ddf_b200_take_fault() == 0
 
 
+def test_noalloc_small_problems_and_single_gradients():
+    """Small problems, where both entry points choose the generic kernels, and calls that ask
+    for one gradient only (the limit and the scratch concern the spatial-filter gradient
+    alone): still bit-identical to ddf_b200_backward."""
+    from ddfnet_b200 import _lib
+    L = _lib.load()
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    shape = (2, 6, 9, 11, 3, 1, 1)
+    B, C, H, W, k, d, s = shape
+    assert L.ddf_b200_plan(B, C, H, W, k, d, s, 0, 0, 1) == _lib.VARIANT_GENERIC
+    x, cf, sf, go = make_inputs(B, C, H, W, k, s, torch.float32, seed=41)
+    tensors = tuple(t.to(dev) for t in (go, x, cf, sf))
+    want = _call(L, False, tensors, shape, 0, 0, _lib)
+    for attempt in range(2):
+        got = _call(L, True, tensors, shape, 0, 0, _lib)
+        for name, g, w in zip(("grad_x", "grad_cf", "grad_sf"), got, want):
+            assert torch.equal(g, w), f"{name} differs from ddf_b200_backward on a small problem"
+    # grad_cf only, on a problem whose grad_sf scratch would exceed the built-in array
+    big = (128, 64, 28, 28, 5, 1, 1)
+    B, C, H, W, k, d, s = big
+    x, cf, sf, go = (t.to(dev) for t in make_inputs(B, C, H, W, k, s, torch.float32, seed=6))
+    gcf_a, gcf_b = torch.empty_like(cf), torch.empty_like(cf)
+    rc = L.ddf_b200_backward_noalloc(go.data_ptr(), x.data_ptr(), cf.data_ptr(), sf.data_ptr(), None,
+                                     gcf_a.data_ptr(), None, B, C, H, W, k, d, s, 0, 0, stream)
+    assert rc == 0, L.ddf_b200_strerror(rc)
+    rc = L.ddf_b200_backward(go.data_ptr(), x.data_ptr(), cf.data_ptr(), sf.data_ptr(), None, gcf_b.data_ptr(),
+                             None, None, 0, B, C, H, W, k, d, s, 0, 0, _lib.VARIANT_AUTO, stream)
+    assert rc == 0, L.ddf_b200_strerror(rc)      # no workspace needed without grad_sf
+    torch.cuda.synchronize()
+    assert torch.equal(gcf_a, gcf_b)
+    assert L.ddf_b200_take_fault() == 0
+
+
 def test_noalloc_refuses_problems_beyond_its_scratch():
     from ddfnet_b200 import _lib
     L = _lib.load()
