@@ -21,7 +21,7 @@ static int bwd_pixels(const Problem& p, int sm_count, BwdGeometry& g) {
         if (P == 8) built = (k == 3 && d == 1 && s == 1);
         else if (k == 3 && d == 1) built = (s == 1 || s == 2);
         else if (k == 3 && d == 2 && s == 1) built = P >= 2;
-        else if (k == 5 && (d == 1 || d == 2) && s == 1) built = P == 2;
+        else if (k == 5 && (d == 1 || d == 2) && s == 1) built = P == 2 || P == 4;
         if (!built) continue;
         // the element-wise (sub-word) path of 2-byte types covers a halo of one only
         if (P * s * (p.dtype == DDF_B200_F32 ? 4 : 2) < 4 && (k - 1) / 2 * d > 1) continue;
