@@ -2,7 +2,7 @@
 """Benchmark of the DDF forward at the ddf_resnet50 stage shapes.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload op|model] [--detail PATH]
+                    [--workload op|model|backward|sfnorm|probe] [--detail PATH]
 
 One "step" is the whole sweep: 7 stage shapes x {bf16, f16} x {mul, add} = 28
 DDF forward calls at B = 128, k = 3, d = 1 (stride-1 shapes (C,H) = (64,56),
@@ -18,6 +18,12 @@ describes the kernel instance that takes the largest share of the step;
 reference has no CPU implementation) on a bounded sample.  With N > 1 every rank
 runs the same sweep on its own GPU (the op shards along the batch with no
 collective) and the value is the aggregate.
+
+The same line also carries, beside the headline: `backward` (configs[2]: all three
+gradients, 16 cases, GB/s and fraction of the HBM roofline per case), `model`
+(ddf_mul_resnet50 inference, float16, GLOBAL batch 256 split over the N ranks, images/s),
+`launch_floor_us` (an empty kernel replayed from a CUDA graph) and, per shape,
+`floor_ratio` = (launch floor + bytes / peak) / measured time.
 """
 from __future__ import annotations
 
@@ -123,24 +129,28 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------ CPU legs
-def cpu_sweep_seconds(sample_batch, threads=None):
-    """Times the float32 CPU oracle over the sweep's 7 shapes x 2 modes at a
-    reduced batch.  Returns (seconds, 2-byte algorithmic bytes, threads used)."""
+def cpu_sweep_seconds(sample_batch, threads=None, min_seconds=0.0):
+    """Times the float32 CPU oracle over the sweep's 7 shapes x 2 modes at the given batch,
+    repeating the whole sweep until `min_seconds` of CPU work have been timed.  Returns
+    (seconds, 2-byte algorithmic bytes, threads used, repetitions)."""
     from oracle import ddf_oracle
     # All host cores unless told otherwise: torchrun exports OMP_NUM_THREADS=1 to its workers,
     # which would otherwise leave the CPU arm on a single thread.
     ddf_oracle.set_threads(threads or len(os.sched_getaffinity(0)))
     used = ddf_oracle.max_threads()
-    total_s, total_b = 0.0, 0
-    for i, (C, H, s) in enumerate(SHAPES):
-        x, cf, sf = make_case(C, H, s, torch.float32, sample_batch, None, 10 + i)
-        for mode in ("mul", "add"):
-            ddf_oracle.forward(x[:1], cf[:1], sf[:1], K, D, s, mode)  # page in
-            t0 = time.perf_counter()
-            ddf_oracle.forward(x, cf, sf, K, D, s, mode)
-            total_s += time.perf_counter() - t0
-            total_b += algorithmic_bytes(sample_batch, C, H, s, 2)
-    return total_s, total_b, used
+    inputs = [make_case(C, H, s, torch.float32, sample_batch, None, 10 + i) for i, (C, H, s) in enumerate(SHAPES)]
+    for (x, cf, sf), (_C, _H, s) in zip(inputs, SHAPES):
+        ddf_oracle.forward(x[:1], cf[:1], sf[:1], K, D, s, "mul")  # page in
+    total_s, total_b, reps = 0.0, 0, 0
+    while reps == 0 or total_s < min_seconds:
+        for (x, cf, sf), (C, H, s) in zip(inputs, SHAPES):
+            for mode in ("mul", "add"):
+                t0 = time.perf_counter()
+                ddf_oracle.forward(x, cf, sf, K, D, s, mode)
+                total_s += time.perf_counter() - t0
+                total_b += algorithmic_bytes(sample_batch, C, H, s, 2)
+        reps += 1
+    return total_s, total_b, used, reps
 
 
 def run_reference(args, rank, world):
@@ -149,13 +159,15 @@ def run_reference(args, rank, world):
     arithmetic -- on all host threads, on a bounded sample of the same sweep."""
     if rank != 0:
         return
-    sample_batch = 16
-    for _ in range(max(1, args.warmup)):
-        cpu_sweep_seconds(2)
-    secs, nbytes, used = 0.0, 0, 1
-    for _ in range(args.steps):
-        s_, b_, used = cpu_sweep_seconds(sample_batch)
-        secs += s_; nbytes += b_
+    # one step = the full-size sweep (B = 128: 0.4 GB of float32 inputs per shape set, far larger
+    # than the host caches); at least about five seconds of CPU work are timed in all
+    sample_batch = BATCH
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_sweep_seconds(8)
+    secs, nbytes, used, reps = 0.0, 0, 1, 0
+    for i in range(args.steps):
+        s_, b_, used, r_ = cpu_sweep_seconds(sample_batch, min_seconds=5.0 / args.steps)
+        secs += s_; nbytes += b_; reps += r_
     gbs = nbytes / secs / 1e9
     line = {
         "impl": "reference", "metric": "ddf_forward_hbm_gbs", "value": gbs, "unit": "GB/s",
@@ -166,11 +178,16 @@ def run_reference(args, rank, world):
         "data": "synthetic",
         "config": workload_config(),
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": used, "kind": "port",
-                         "sample": f"7 shapes x (mul, add) at B={sample_batch} of {BATCH}, float32, "
-                                   f"{os.cpu_count()} logical CPUs, OpenMP threads={used}"},
+                         "sample": f"7 shapes x (mul, add) at the full B={sample_batch}, float32, {reps} sweeps, "
+                                   f"{secs:.1f} s, {os.cpu_count()} logical CPUs, OpenMP threads={used}"},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
+
+
+def kernel_name(H, stride):
+    """Which forward kernel serves a 2-byte sweep shape (see ring_inst.inc)."""
+    return "ring_kernel" if (stride == 1 and H in (56, 28, 14)) or (stride == 2 and H == 28) else "stream_kernel"
 
 
 def workload_config():
@@ -249,6 +266,7 @@ def run_ours(args, rank, world, local_rank):
 
         # per-call durations: each call replayed alone from its own graph over rotating
         # buffer sets larger than L2, timed with CUDA events
+        floor_us = launch_floor_us(L)
         per_shape = []
         if rank == 0 and not args.quick:
             for (mode, dtname, C, H, s, x, cf, sf) in cases:
@@ -272,7 +290,8 @@ def run_ours(args, rank, world, local_rank):
                 us = a.elapsed_time(b) * 1e3 / (reps * nsets)
                 per_shape.append({"C": C, "H": H, "stride": s, "dtype": dtname, "combine": mode,
                                   "us": round(us, 3), "bytes": nb, "gbs": round(nb / us / 1e3, 1),
-                                  "frac": round(nb / us / 1e3 / peak, 4)})
+                                  "frac": round(nb / us / 1e3 / peak, 4),
+                                  "floor_ratio": round((floor_us + nb / peak / 1e3) / us, 4)})
                 del g, held, sets
         clocks = sampler.stop() if rank == 0 else None
 
@@ -313,24 +332,66 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize()
         e2e_ms = max(a.elapsed_time(b), (time.perf_counter() - t0) * 1e3)
 
+        # the copies alone (same pinned buffers, same bytes, no kernels): what the host side
+        # of this box delivers to this rank while all ranks copy at once
+        up = {k_: tuple(torch.empty_like(t, device=dev) for t in v[:3]) for k_, v in host_sets.items()}
+        dn = {k_: {m: torch.empty_like(o, device=dev) for m, o in v[3].items()} for k_, v in host_sets.items()}
+        s_up, s_dn = torch.cuda.Stream(), torch.cuda.Stream()
+
+        def copy_step():
+            with torch.cuda.stream(s_up):
+                for _rep in range(2):          # every input set is uploaded once per combine mode
+                    for k_, v in host_sets.items():
+                        for src, dst in zip(v[:3], up[k_]):
+                            dst.copy_(src, non_blocking=True)
+            with torch.cuda.stream(s_dn):
+                for k_, v in host_sets.items():
+                    for m, o in v[3].items():
+                        o.copy_(dn[k_][m], non_blocking=True)
+            s_up.synchronize()
+            s_dn.synchronize()
+
+        copy_step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            copy_step()
+        copy_ms = (time.perf_counter() - t0) * 1e3
+        del up, dn
+
+    # configs[2] backward on rank 0 (the other ranks wait), then the model at global batch 256
+    backward = None
+    model = None
+    if not args.quick:
+        if rank == 0:
+            backward = measure_backward(L, dev, peak, max(2, min(args.steps, 5)), with_sweep_shapes=False)
+        if world > 1:
+            dist.barrier()
+        del graph, keep, tensors, cases
+        torch.cuda.empty_cache()
+        model = measure_model(rank, world, local_rank, "ddf_mul_resnet50", max(5, min(args.steps, 20)), 3)
+
     if world > 1:
-        t = torch.tensor([elapsed_ms, e2e_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([elapsed_ms, e2e_ms, copy_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_ms = t.tolist()
+        elapsed_ms, e2e_ms, copy_ms = t.tolist()
     if rank != 0:
         return
 
     ms_per_step = elapsed_ms / args.steps
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
     e2e_value = world * step_bytes / (e2e_ms / e2e_steps * 1e-3) / 1e9
+    copy_value = world * step_bytes / (copy_ms / e2e_steps * 1e-3) / 1e9
 
     # dominant kernel instance = largest share of the step
     roof = None
     if per_shape:
         dom = max(per_shape, key=lambda r: r["us"])
         roof = {"bound": "hbm",
-                "kernel": f"stream_kernel fwd C={dom['C']} H={dom['H']} s={dom['stride']} "
-                          f"{dom['dtype']} {dom['combine']}",
+                "kernel": f"{kernel_name(dom['H'], dom['stride'])} fwd C={dom['C']} H={dom['H']} "
+                          f"s={dom['stride']} {dom['dtype']} {dom['combine']}",
                 "achieved": dom["gbs"], "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
                 "frac": round(dom["gbs"] / peak, 4), "frac_of_8000": round(dom["gbs"] / 8000.0, 4),
                 "traffic": None, "us_per_launch": dom["us"], "algorithmic_bytes": dom["bytes"]}
@@ -345,12 +406,11 @@ def run_ours(args, rank, world, local_rank):
 
     cpu = None
     if not args.quick:
-        sample_batch = 16
-        cpu_sweep_seconds(2)
-        secs, nbytes, used = cpu_sweep_seconds(sample_batch)
+        cpu_sweep_seconds(8)
+        secs, nbytes, used, reps = cpu_sweep_seconds(BATCH, min_seconds=10.0)
         cpu = {"value": round(nbytes / secs / 1e9, 3), "unit": "GB/s", "cores": used, "kind": "port",
-               "sample": f"7 shapes x (mul, add) at B={sample_batch} of {BATCH}, float32 CPU oracle, "
-                         f"{os.cpu_count()} logical CPUs, OpenMP threads={used}, {secs:.2f} s"}
+               "sample": f"7 shapes x (mul, add) at the full B={BATCH}, float32 CPU oracle, {reps} sweeps, "
+                         f"{secs:.1f} s, {os.cpu_count()} logical CPUs, OpenMP threads={used}"}
 
     line = {
         "metric": "ddf_forward_hbm_gbs", "value": round(value, 1), "unit": "GB/s",
@@ -362,7 +422,15 @@ def run_ours(args, rank, world, local_rank):
         "frac_of_8000": round(value / world / 8000.0, 4),
         "roofline": roof, "cpu_baseline": cpu,
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+                "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                "per_rank_h2d_gbs": round(h2d / (e2e_ms / e2e_steps * 1e-3) / 1e9, 2),
+                "per_rank_d2h_gbs": round(d2h / (e2e_ms / e2e_steps * 1e-3) / 1e9, 2),
+                "copies_only": {"value": round(copy_value, 2), "unit": "GB/s",
+                                "what": "the same pinned-buffer uploads and downloads with no kernels, all ranks "
+                                        "at once: the ceiling the host side of this box sets",
+                                "e2e_over_copies_only": round(e2e_value / copy_value, 3)}},
+        "launch_floor_us": round(floor_us, 3) if per_shape else None,
+        "backward": backward, "model": model,
         "gpu_launches": int(launches), "clocks": clocks,
         "per_shape": per_shape,
     }
@@ -372,121 +440,102 @@ def run_ours(args, rank, world, local_rank):
             json.dump(line, f, indent=1)
 
 
-def run_backward(args, rank, world, local_rank):
+def measure_backward(L, dev, peak, steps, with_sweep_shapes=True):
     """configs[2]: DDF backward (all three gradients) at B=64, C=256, 28x28, k in
     {3, 5}, d in {1, 2}, stride 1, mul and add, float32 and bfloat16, through the
     C ABI with caller-allocated outputs and workspace.  Per case: its own CUDA
     graph over rotating buffer sets larger than L2, CUDA events."""
     from ddfnet_b200 import _lib
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    L = _lib.load()
-    peak, peak_kind = peaks()
     B, C, H = 64, 256, 28
     rows, total_bytes, total_us = [], 0, 0.0
-    for dtname, dtype, dtc in (("f32", torch.float32, _lib.F32), ("bf16", torch.bfloat16, _lib.BF16)):
-        es = 4 if dtname == "f32" else 2
-        for k in (3, 5):
-            for d in (1, 2):
-                g = torch.Generator().manual_seed(300 + k + d)
-                mk = lambda *shape: torch.randn(*shape, generator=g)
-                base = (mk(B, C, H, H), mk(B, C, H, H).relu_(), mk(B, C, k, k) / 3, mk(B, k * k, H, H) / 3)
-                nb = es * (B * C * H * H + 2 * B * C * H * H + 2 * B * C * k * k + 2 * B * k * k * H * H)
-                nsets = max(3, (2 * L2_BYTES) // nb + 2)
-                sets = []
-                for _ in range(nsets):
-                    go, x, cf, sf = (t.to(dev, dtype) for t in base)
-                    sets.append((go, x, cf, sf, torch.empty_like(x), torch.empty_like(cf), torch.empty_like(sf)))
-                for mode, comb in (("mul", _lib.MUL), ("add", _lib.ADD)):
-                    wsb = int(L.ddf_b200_backward_workspace(B, C, H, H, k, d, 1, comb, dtc, _lib.VARIANT_AUTO))
-                    ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=dev)
 
-                    def call(st):
-                        go, x, cf, sf, gx, gcf, gsf = st
-                        _lib.check(L.ddf_b200_backward(
-                            go.data_ptr(), x.data_ptr(), cf.data_ptr(), sf.data_ptr(), gx.data_ptr(),
-                            gcf.data_ptr(), gsf.data_ptr(), ws.data_ptr(), wsb, B, C, H, H, k, d, 1, comb,
-                            dtc, _lib.VARIANT_AUTO, torch.cuda.current_stream().cuda_stream))
-
-                    for st in sets:
-                        call(st)
-                    torch.cuda.synchronize()
-                    gr = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(gr):
-                        for st in sets:
-                            call(st)
-                    for _ in range(3):
-                        gr.replay()
-                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    a.record()
-                    for _ in range(args.steps):
-                        gr.replay()
-                    b.record()
-                    torch.cuda.synchronize()
-                    us = a.elapsed_time(b) * 1e3 / (args.steps * nsets)
-                    rows.append({"dtype": dtname, "k": k, "d": d, "combine": mode, "us": round(us, 2),
-                                 "bytes": nb, "gbs": round(nb / us / 1e3, 1),
-                                 "frac": round(nb / us / 1e3 / peak, 4),
-                                 "plan": int(L.ddf_b200_plan(B, C, H, H, k, d, 1, comb, dtc, 1))})
-                    total_bytes += nb
-                    total_us += us
-                del sets
-    # The sweep's own shapes (bf16, mul, k = 3), not part of `value`: which of them the
-    # streaming backward covers and what the others cost on the generic kernels.
-    shape_rows = []
-    for (C2, H2, s2) in SHAPES:
-        k, d, dtc, dtype, es = 3, 1, _lib.BF16, torch.bfloat16, 2
-        oh = H2 // s2
-        g = torch.Generator().manual_seed(700 + C2 + s2)
-        base = (torch.randn(B, C2, oh, oh, generator=g), torch.randn(B, C2, H2, H2, generator=g).relu_(),
-                torch.randn(B, C2, k, k, generator=g) / 3, torch.randn(B, k * k, oh, oh, generator=g) / 3)
-        nb = es * (B * C2 * oh * oh + 2 * B * C2 * H2 * H2 + 2 * B * C2 * k * k + 2 * B * k * k * oh * oh)
+    def time_case(Bc, Cc, Hc, k, d, s2, comb, dtc, dtype, es, seed):
+        oh = Hc // s2
+        g = torch.Generator().manual_seed(seed)
+        mk = lambda *shape: torch.randn(*shape, generator=g)
+        base = (mk(Bc, Cc, oh, oh), mk(Bc, Cc, Hc, Hc).relu_(), mk(Bc, Cc, k, k) / 3, mk(Bc, k * k, oh, oh) / 3)
+        nb = es * (Bc * Cc * oh * oh + 2 * Bc * Cc * Hc * Hc + 2 * Bc * Cc * k * k + 2 * Bc * k * k * oh * oh)
         nsets = max(3, (2 * L2_BYTES) // nb + 2)
         sets = []
         for _ in range(nsets):
             go, x, cf, sf = (t.to(dev, dtype) for t in base)
             sets.append((go, x, cf, sf, torch.empty_like(x), torch.empty_like(cf), torch.empty_like(sf)))
-        wsb = int(L.ddf_b200_backward_workspace(B, C2, H2, H2, k, d, s2, _lib.MUL, dtc, _lib.VARIANT_AUTO))
-        ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=dev)
+        out = {}
+        for mode, cmb in comb:
+            wsb = int(L.ddf_b200_backward_workspace(Bc, Cc, Hc, Hc, k, d, s2, cmb, dtc, _lib.VARIANT_AUTO))
+            ws = torch.empty(max(wsb, 1), dtype=torch.uint8, device=dev)
 
-        def call2(st):
-            go, x, cf, sf, gx, gcf, gsf = st
-            _lib.check(L.ddf_b200_backward(
-                go.data_ptr(), x.data_ptr(), cf.data_ptr(), sf.data_ptr(), gx.data_ptr(), gcf.data_ptr(),
-                gsf.data_ptr(), ws.data_ptr(), wsb, B, C2, H2, H2, k, d, s2, _lib.MUL, dtc,
-                _lib.VARIANT_AUTO, torch.cuda.current_stream().cuda_stream))
+            def call(st):
+                go, x, cf, sf, gx, gcf, gsf = st
+                _lib.check(L.ddf_b200_backward(
+                    go.data_ptr(), x.data_ptr(), cf.data_ptr(), sf.data_ptr(), gx.data_ptr(),
+                    gcf.data_ptr(), gsf.data_ptr(), ws.data_ptr(), wsb, Bc, Cc, Hc, Hc, k, d, s2, cmb,
+                    dtc, _lib.VARIANT_AUTO, torch.cuda.current_stream().cuda_stream))
 
-        for st in sets:
-            call2(st)
-        torch.cuda.synchronize()
-        gr = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(gr):
             for st in sets:
-                call2(st)
-        for _ in range(3):
-            gr.replay()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(args.steps):
-            gr.replay()
-        b.record()
-        torch.cuda.synchronize()
-        us = a.elapsed_time(b) * 1e3 / (args.steps * nsets)
-        shape_rows.append({"C": C2, "H": H2, "stride": s2, "us": round(us, 1), "gbs": round(nb / us / 1e3, 1),
-                           "frac": round(nb / us / 1e3 / peak, 4),
-                           "filter_gradients": "streaming" if wsb > 0 else "generic",
-                           "grad_x": "streaming" if s2 == 1 else "stride-2 kernel"})
+                call(st)
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for st in sets:
+                    call(st)
+            for _ in range(3):
+                gr.replay()
+            a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a_.record()
+            for _ in range(steps):
+                gr.replay()
+            b_.record()
+            torch.cuda.synchronize()
+            out[mode] = (a_.elapsed_time(b_) * 1e3 / (steps * nsets), nb, wsb)
+            del gr
         del sets
+        return out
+
+    for dtname, dtype, dtc in (("f32", torch.float32, _lib.F32), ("bf16", torch.bfloat16, _lib.BF16)):
+        es = 4 if dtname == "f32" else 2
+        for k in (3, 5):
+            for d in (1, 2):
+                res = time_case(B, C, H, k, d, 1, (("mul", _lib.MUL), ("add", _lib.ADD)), dtc, dtype, es, 300 + k + d)
+                for mode, (us, nb, _w) in res.items():
+                    rows.append({"dtype": dtname, "k": k, "d": d, "combine": mode, "us": round(us, 2),
+                                 "bytes": nb, "gbs": round(nb / us / 1e3, 1),
+                                 "frac": round(nb / us / 1e3 / peak, 4)})
+                    total_bytes += nb
+                    total_us += us
+    # The sweep's own shapes (bf16, mul, k = 3), not part of `value`.
+    shape_rows = []
+    if with_sweep_shapes:
+        for (C2, H2, s2) in SHAPES:
+            res = time_case(B, C2, H2, 3, 1, s2, (("mul", _lib.MUL),), _lib.BF16, torch.bfloat16, 2, 700 + C2 + s2)
+            us, nb, wsb = res["mul"]
+            shape_rows.append({"C": C2, "H": H2, "stride": s2, "us": round(us, 1), "gbs": round(nb / us / 1e3, 1),
+                               "frac": round(nb / us / 1e3 / peak, 4),
+                               "filter_gradients": "streaming" if wsb > 0 else "generic"})
+    return {"value": round(total_bytes / total_us / 1e3, 1), "unit": "GB/s",
+            "workload": "configs[2]: DDF backward, B=64, C=256, 28x28, k 3/5, d 1/2, mul/add, f32 + bf16; "
+                        "rotating buffer sets larger than L2",
+            "ms_all_cases": round(total_us / 1e3, 4), "min_frac": min(r["frac"] for r in rows),
+            "frac": round(total_bytes / total_us / 1e3 / peak, 4),
+            "per_case": rows, "sweep_shapes_bf16_mul_B64": shape_rows}
+
+
+def run_backward(args, rank, world, local_rank):
+    from ddfnet_b200 import _lib
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    L = _lib.load()
+    peak, peak_kind = peaks()
+    r = measure_backward(L, dev, peak, args.steps)
     if rank == 0:
         print(json.dumps({
-            "metric": "ddf_backward_hbm_gbs", "value": round(total_bytes / total_us / 1e3, 1), "unit": "GB/s",
-            "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": round(total_us / 1e3, 4),
+            "metric": "ddf_backward_hbm_gbs", "value": r["value"], "unit": "GB/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": r["ms_all_cases"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32+bf16 I/O, f32 arithmetic", "data": "synthetic",
-            "config": {"workload": "configs[2]: DDF backward, B=64, C=256, 28x28, k 3/5, d 1/2, mul/add",
-                       "l2": "rotating buffer sets larger than L2"},
-            "peak": peak, "peak_kind": f"of {peak_kind}", "per_case": rows,
-            "sweep_shapes_bf16_mul_B64": shape_rows}))
+            "config": {"workload": r["workload"]},
+            "peak": peak, "peak_kind": f"of {peak_kind}", "min_frac": r["min_frac"], "per_case": r["per_case"],
+            "sweep_shapes_bf16_mul_B64": r["sweep_shapes_bf16_mul_B64"]}))
 
 
 def run_sfnorm(args, rank, world, local_rank):
@@ -546,41 +595,42 @@ def run_sfnorm(args, rank, world, local_rank):
             "peak": peak, "peak_kind": f"of {peak_kind}", "per_shape": rows}))
 
 
-def run_model(args, rank, world, local_rank):
-    """Whole-network inference throughput (images/s) of the DDF-ResNet harness,
-    batch-sharded over the ranks; logits are all-gathered once for checking."""
+def measure_model(rank, world, local_rank, name, steps, warmup, channels_last=True, fold_bn="fused",
+                  unfused_norm=False, no_graph=False):
+    """Whole-network inference throughput (images/s) of the DDF-ResNet harness at the
+    model's GLOBAL batch, batch-sharded over the ranks (strong scaling); logits are
+    all-gathered once, outside the timed region, for checking."""
     import torch.distributed as dist
     from ddfnet_b200.resnet import MODELS
     from ddfnet_b200.shard import batch_slice, gather_batch
 
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    name = args.model
     dtype, gbatch = MODEL_CFG[name]
     lo, hi = batch_slice(gbatch, rank, world)
     torch.manual_seed(0)
     model = MODELS[name]().to(dev).eval()
-    if args.fold_bn:
+    if fold_bn:
         from ddfnet_b200.resnet import fold_batchnorm
-        fold_batchnorm(model, fuse_activations=args.fold_bn == "fused")
+        fold_batchnorm(model, fuse_activations=fold_bn == "fused")
     model = model.to(dtype)
-    if args.channels_last:
+    if channels_last:
         model = model.to(memory_format=torch.channels_last)
     for m in model.ddf_layers():
-        m.fuse_filter_norm = not args.unfused_norm
-        m.fuse_channel_branch = not args.unfused_norm
+        m.fuse_filter_norm = not unfused_norm
+        m.fuse_channel_branch = not unfused_norm
     g = torch.Generator().manual_seed(1)
     x = torch.randn(gbatch, 3, 224, 224, generator=g)[lo:hi].to(dev, dtype)
-    if args.channels_last:
+    if channels_last:
         x = x.contiguous(memory_format=torch.channels_last)
     with torch.no_grad():
-        for _ in range(max(args.warmup, 3)):
+        for _ in range(max(warmup, 3)):
             y = model(x)
         torch.cuda.synchronize()
-        # The whole network as one CUDA graph: at 32 images per GPU the ~600 small
+        # The whole network as one CUDA graph: at 32 images per GPU the ~300 small
         # kernels of a forward pass are otherwise bound by launch overhead.
         graphed = False
-        if not args.no_graph:
+        if not no_graph:
             try:
                 graph = torch.cuda.CUDAGraph()
                 side = torch.cuda.Stream()
@@ -598,12 +648,15 @@ def run_model(args, rank, world, local_rank):
         run = graph.replay if graphed else (lambda: model(x))
         if world > 1:
             dist.barrier()
+        torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             run()
         b.record()
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         ms = a.elapsed_time(b)
         if not graphed:
             y = model(x)
@@ -612,20 +665,72 @@ def run_model(args, rank, world, local_rank):
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = t.item()
+    return {"name": name, "images_per_s": round(gbatch * steps / (ms * 1e-3), 1), "global_batch": gbatch,
+            "per_gpu_batch": hi - lo, "ms_per_step": round(ms / steps, 3), "steps": steps,
+            "dtype": str(dtype).replace("torch.", ""), "scaling": "strong", "cuda_graph": graphed,
+            "flags": {"filter_branches": "reference module sequence (torch ops)" if unfused_norm
+                      else "spatial FilterNorm fused into the DDF kernel, channel branch as one kernel",
+                      "memory_format": "channels_last around the DDF layers" if channels_last else "NCHW",
+                      "batchnorm": {None: "as built", "plain": "folded into the preceding convolutions",
+                                    "fused": "folded; conv+bias(+shortcut)+ReLU as single cuDNN calls"}[fold_bn]},
+            "logits_finite": bool(torch.isfinite(logits).all()), "logits_shape": list(logits.shape)}
+
+
+def run_model(args, rank, world, local_rank):
+    r = measure_model(rank, world, local_rank, args.model, args.steps, args.warmup, args.channels_last,
+                      args.fold_bn, args.unfused_norm, args.no_graph)
     if rank == 0:
         print(json.dumps({
-            "metric": f"{name}_images_per_s", "value": round(gbatch * args.steps / (ms * 1e-3), 1),
+            "metric": f"{r['name']}_images_per_s", "value": r["images_per_s"],
             "unit": "images/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": str(dtype).replace("torch.", ""), "data": "synthetic",
-            "config": {"workload": f"{name} inference, global batch {gbatch}, 224x224, random init",
-                       "per_gpu_batch": hi - lo, "cuda_graph": graphed,
-                       "filter_branches": "reference module sequence (torch ops)" if args.unfused_norm
-                       else "spatial FilterNorm fused into the DDF kernel, channel branch as one kernel",
-                       "memory_format": "channels_last around the DDF layers" if args.channels_last else "NCHW",
-                       "batchnorm": {None: "as built", "plain": "folded into the preceding convolutions",
-                                     "fused": "folded; conv+bias(+shortcut)+ReLU as single cuDNN calls"}[args.fold_bn]},
-            "logits_finite": bool(torch.isfinite(logits).all()), "logits_shape": list(logits.shape)}))
+            "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": r["dtype"], "data": "synthetic",
+            "config": {"workload": f"{r['name']} inference, global batch {r['global_batch']}, 224x224, random init",
+                       "per_gpu_batch": r["per_gpu_batch"], "cuda_graph": r["cuda_graph"], **r["flags"]},
+            "logits_finite": r["logits_finite"], "logits_shape": r["logits_shape"]}))
+
+
+def launch_floor_us(L, reps=200):
+    """Time per launch of an empty kernel replayed from a CUDA graph."""
+    g = torch.cuda.CUDAGraph()
+    stream = torch.cuda.current_stream()
+    L.ddf_b200_noop(stream.cuda_stream)
+    torch.cuda.synchronize()
+    with torch.cuda.graph(g):
+        for _ in range(50):
+            L.ddf_b200_noop(torch.cuda.current_stream().cuda_stream)
+    for _ in range(3):
+        g.replay()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps // 50):
+        g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / (reps // 50 * 50)
+
+
+def run_probe(args, rank, world, local_rank):
+    """Instruction issue rates and the launch floor (the numbers the roofline discussion uses)."""
+    import ctypes
+    from ddfnet_b200 import _lib
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    L = _lib.load()
+    nbytes = int(L.ddf_b200_rate_probe_bytes())
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    names = ["ffma_repeated_multiplicands", "ffma_three_distinct_registers", "mixed_fma_bf16", "mixed_fma_f16",
+             "fma_f32x2", "lop3"]
+    rates = {}
+    for mode, nm in enumerate(names):
+        v = ctypes.c_double(0.0)
+        _lib.check(L.ddf_b200_rate_probe(mode, scratch.data_ptr(), nbytes, 1024, ctypes.byref(v),
+                                         torch.cuda.current_stream().cuda_stream))
+        rates[nm] = round(v.value, 3)
+    if rank == 0:
+        print(json.dumps({"metric": "warp_instructions_per_ns_per_sm", "rates": rates,
+                          "launch_floor_us": round(launch_floor_us(L), 3),
+                          "note": "4 schedulers per SM at 1.965 GHz issue at most 7.86 warp instructions per ns"}))
 
 
 def run_ncu_case(spec):
@@ -701,7 +806,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="op", choices=["op", "model", "backward", "sfnorm"])
+    ap.add_argument("--workload", default="op", choices=["op", "model", "backward", "sfnorm", "probe"])
     ap.add_argument("--model", default="ddf_mul_resnet50", choices=sorted(MODEL_CFG))
     ap.add_argument("--quick", action="store_true",
                     help="op workload: skip the per-call timings and the CPU baseline (scaling runs)")
@@ -746,6 +851,8 @@ def main():
             run_backward(args, rank, world, local_rank)
         elif args.workload == "sfnorm":
             run_sfnorm(args, rank, world, local_rank)
+        elif args.workload == "probe":
+            run_probe(args, rank, world, local_rank)
         else:
             run_ours(args, rank, world, local_rank)
     finally:

@@ -25,6 +25,7 @@ SYMBOLS = (
     "ddf_b200_forward_sfnorm", "ddf_b200_nhwc_to_nchw", "ddf_b200_nchw_to_nhwc", "ddf_b200_nhwc_to_nchw_affine",
     "ddf_b200_channel_filter", "ddf_b200_channel_filter_slice",
     "ddf_b200_frontend_tiles", "ddf_b200_pack_frontend", "ddf_b200_forward_waitlimit",
+    "ddf_b200_noop", "ddf_b200_rate_probe_bytes", "ddf_b200_rate_probe",
 )
 
 
@@ -53,6 +54,12 @@ def load() -> ctypes.CDLL:
         L.ddf_b200_forward.argtypes = [vp] * 4 + [i] * 10 + [vp]
         L.ddf_b200_forward_waitlimit.restype = i
         L.ddf_b200_forward_waitlimit.argtypes = [vp] * 4 + [i] * 9 + [ctypes.c_longlong, i, vp]
+        L.ddf_b200_noop.restype = i
+        L.ddf_b200_noop.argtypes = [vp]
+        L.ddf_b200_rate_probe_bytes.restype = sz
+        L.ddf_b200_rate_probe_bytes.argtypes = []
+        L.ddf_b200_rate_probe.restype = i
+        L.ddf_b200_rate_probe.argtypes = [i, vp, sz, i, ctypes.POINTER(ctypes.c_double), vp]
         L.ddf_b200_forward_sfnorm.restype = i
         L.ddf_b200_forward_sfnorm.argtypes = [vp] * 4 + [i] * 10 + [ctypes.c_double, vp]
         L.ddf_b200_nhwc_to_nchw.restype = i

@@ -118,6 +118,21 @@ int ddf_b200_forward_waitlimit(const void* x, const void* cf, const void* sf, vo
                                int combine, int dtype, long long wait_cycles, int starve,
                                void* stream);
 
+/*
+ * Measurement aids (no counterpart in the reference, which measures with wall-clock loops,
+ * test_time.py:11-51).  ddf_b200_noop enqueues an empty kernel: replayed from a CUDA graph
+ * it gives the launch floor the small shapes are compared with.  ddf_b200_rate_probe
+ * measures how many warp instructions of one kind an SM issues per nanosecond
+ * (mode 0 float FMA with repeated multiplicands, 1 float FMA with three distinct register
+ * operands, 2 / 3 the mixed-precision FMA with bf16 / f16 multiplicands, 4 packed
+ * fma.f32x2, 5 lop3); it needs ddf_b200_rate_probe_bytes() of scratch and, unlike every
+ * other call, waits for its own kernels before it returns.
+ */
+int ddf_b200_noop(void* stream);
+size_t ddf_b200_rate_probe_bytes(void);
+int ddf_b200_rate_probe(int mode, void* scratch, size_t scratch_bytes, int iters,
+                        double* warp_instr_per_ns_per_sm, void* stream);
+
 /* Which variant (GENERIC or STREAM) AUTO resolves to for this problem; pointers
  * are assumed 16-byte aligned.  `backward` = 0 for the forward, 1 for the backward.
  * Returns a DDF_B200_VARIANT_* value, or a negative status. */
