@@ -25,6 +25,7 @@ SYMBOLS = (
     "ddf_b200_forward_sfnorm", "ddf_b200_nhwc_to_nchw", "ddf_b200_nchw_to_nhwc", "ddf_b200_nhwc_to_nchw_affine",
     "ddf_b200_channel_filter", "ddf_b200_channel_filter_slice",
     "ddf_b200_frontend_tiles", "ddf_b200_pack_frontend", "ddf_b200_forward_waitlimit",
+    "ddf_b200_forward_nhwc", "ddf_b200_pool_nhwc_tiles", "ddf_b200_pool_nhwc",
     "ddf_b200_noop", "ddf_b200_rate_probe_bytes", "ddf_b200_rate_probe",
 )
 
@@ -54,6 +55,13 @@ def load() -> ctypes.CDLL:
         L.ddf_b200_forward.argtypes = [vp] * 4 + [i] * 10 + [vp]
         L.ddf_b200_forward_waitlimit.restype = i
         L.ddf_b200_forward_waitlimit.argtypes = [vp] * 4 + [i] * 9 + [ctypes.c_longlong, i, vp]
+        ll = ctypes.c_longlong
+        L.ddf_b200_forward_nhwc.restype = i
+        L.ddf_b200_forward_nhwc.argtypes = [vp] * 7 + [i] * 10 + [ll, ll, ll, i, ctypes.c_double, vp]
+        L.ddf_b200_pool_nhwc_tiles.restype = i
+        L.ddf_b200_pool_nhwc_tiles.argtypes = [i, i]
+        L.ddf_b200_pool_nhwc.restype = i
+        L.ddf_b200_pool_nhwc.argtypes = [vp, vp] + [i] * 5 + [vp]
         L.ddf_b200_noop.restype = i
         L.ddf_b200_noop.argtypes = [vp]
         L.ddf_b200_rate_probe_bytes.restype = sz

@@ -94,29 +94,19 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// The same probe for threads that have nothing else to do: the hardware may park
-// the thread for up to the hinted time (ns) before answering "not yet", which
-// keeps waiting warps from burning issue slots in a spin loop.
-__device__ __forceinline__ bool mbar_test_parked(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(2000u)
-        : "memory");
-    return ok != 0;
-}
 // Bounded wait: gives up after about a second (kWaitCycles SM clocks).  Returns
 // false when the limit ran out (the caller records a fault and leaves); never
-// spins forever.
+// spins forever.  mbarrier.try_wait without a time hint blocks for a short,
+// hardware-chosen time and returns as soon as the phase completes; the hinted form
+// compiles to sleep loops that add microseconds to every stage hand-over.
 constexpr long long kWaitCycles = 2000000000ll;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     if (mbar_test(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
-        if (mbar_test_parked(bar, parity)) return true;
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_test(bar, parity)) return true;
         if (clock64() - t0 > kWaitCycles) return false;
     }
 }

@@ -127,17 +127,11 @@ def pack_frontend(x: torch.Tensor, conv: nn.Conv2d | None = None):
     return x_nchw, raw, pooled
 
 
-def spatial_raw_padded(conv: nn.Conv2d, x: torch.Tensor):
-    """The spatial branch's 1x1 convolution for channels_last inference: the library
-    convolution with its head*k*k output maps zero-padded to a multiple of 16 (several times
-    faster than with 9 maps) and no bias, then the library transpose that drops the padding
-    and adds the bias.  Returns contiguous NCHW (B, G, H', W'), or None when not applicable."""
-    if torch.is_grad_enabled() and (x.requires_grad or conv.weight.requires_grad):
-        return None
-    if (not x.is_cuda or x.is_contiguous() or not x.is_contiguous(memory_format=torch.channels_last)
-            or conv.kernel_size != (1, 1) or conv.bias is None or x.dtype == torch.float64
-            or conv.weight.dtype != x.dtype):
-        return None
+def _padded_spatial_conv(conv: nn.Conv2d):
+    """The spatial branch's 1x1 convolution with its head*k*k output maps zero-padded to a
+    multiple of 16 (the library convolution is several times faster with 16 maps than with 9)
+    and the bias taken out: (padded channels_last weight, ones, float32 bias), cached on the
+    module until the parameters change."""
     g, c = conv.out_channels, conv.in_channels
     gp = (g + 15) // 16 * 16
     key = (conv.weight.data_ptr(), conv.weight._version, conv.bias.data_ptr(), conv.bias._version,
@@ -150,9 +144,27 @@ def spatial_raw_padded(conv: nn.Conv2d, x: torch.Tensor):
         cache = (key, w, torch.ones(g, dtype=torch.float32, device=w.device),
                  conv.bias.detach().float().contiguous())
         conv._ddf_padded = cache
-    _, w, ones, bias = cache
+    return cache[1], cache[2], cache[3]
+
+
+def _spatial_conv_fast_path(conv: nn.Conv2d, x: torch.Tensor) -> bool:
+    if torch.is_grad_enabled() and (x.requires_grad or conv.weight.requires_grad or
+                                    (conv.bias is not None and conv.bias.requires_grad)):
+        return False
+    return (x.is_cuda and not x.is_contiguous() and x.is_contiguous(memory_format=torch.channels_last)
+            and conv.kernel_size == (1, 1) and conv.bias is not None and x.dtype != torch.float64
+            and conv.weight.dtype == x.dtype)
+
+
+def spatial_raw_padded(conv: nn.Conv2d, x: torch.Tensor):
+    """The spatial branch's 1x1 convolution for channels_last inference: the padded library
+    convolution without bias, then the library transpose that drops the padding and adds the
+    bias.  Returns contiguous NCHW (B, G, H', W'), or None when not applicable."""
+    if not _spatial_conv_fast_path(conv, x):
+        return None
+    w, ones, bias = _padded_spatial_conv(conv)
     y = F.conv2d(x, w, None, conv.stride)
-    return to_nchw_affine(y, g, ones, bias)
+    return to_nchw_affine(y, conv.out_channels, ones, bias)
 
 
 def channel_filter_fused(branch: nn.Sequential, x: torch.Tensor, kernel_size: int, pooled=None):
@@ -224,11 +236,38 @@ class DDFPack(nn.Module):
         # (two 1x1 convolutions, ReLU, FilterNorm) runs as one library kernel.
         self.fuse_channel_branch = True
 
+    def forward_channels_last(self, x, out_scale=None, out_shift=None, relu=False):
+        """Inference on a channels_last ``x`` with no layout copy: pooled sums -> channel-branch
+        kernel, padded spatial convolution, and the channels-innermost DDF kernel, which adds
+        the convolution bias, applies the spatial FilterNorm and, if given, a per-channel affine
+        map (float32 ``out_scale`` / ``out_shift``) and ReLU on its store.  Returns a
+        channels_last tensor, or None when the case is outside that path (the caller then uses
+        ``forward``)."""
+        from .nhwc import ddf_nhwc, nhwc_supported, pool_partials
+        k, s = self.kernel_size, self.stride
+        conv, norm = self.spatial_branch[0], self.spatial_branch[1]
+        if not (self.fuse_filter_norm and self.fuse_channel_branch and self.head == 1 and x.dim() == 4
+                and not x.is_contiguous() and nhwc_supported(x, k, self.dilation, s)
+                and x.shape[2] % s == 0 and _spatial_conv_fast_path(conv, x)
+                and not norm.runing_std and not norm.runing_mean):
+            return None
+        channel_filter = channel_filter_fused(self.channel_branch, x, k, pool_partials(x))
+        if channel_filter is None:
+            return None
+        w16, _ones, bias = _padded_spatial_conv(conv)
+        raw = F.conv2d(x, w16, None, conv.stride)          # (B, 16, H', W') channels_last, no bias
+        return ddf_nhwc(x, channel_filter, raw, k, self.dilation, s, self.kernel_combine, sf_bias=bias,
+                        sf_norm_scale=float(norm.std), out_scale=out_scale, out_shift=out_shift, relu=relu)
+
     def forward(self, x):
         b, c, h, w = x.shape
         g = self.head
         k = self.kernel_size
         s = self.stride
+        if x.dim() == 4 and x.is_cuda and not x.is_contiguous():
+            out = self.forward_channels_last(x)   # channels_last inference: no layout copies at all
+            if out is not None:
+                return out
         # The op works on contiguous NCHW.  In a channels_last network the two branches
         # still consume the tensor as it came (their convolutions want that layout) and
         # only the op's operands are converted, by the library's transpose kernel.

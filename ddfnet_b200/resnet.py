@@ -68,8 +68,17 @@ class DDFBottleneck(nn.Module):
         shortcut = x if self.downsample is None else self.downsample(x)
         c1, c3 = self.conv1, self.conv3
         x = torch.cudnn_convolution_relu(x, c1.weight, c1.bias, c1.stride, c1.padding, c1.dilation, 1)
-        x = self.conv2(x)  # DDFPack: contiguous NCHW out
-        if shortcut.is_contiguous(memory_format=torch.channels_last) and not shortcut.is_contiguous():
+        if x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous():
+            # channels_last network: the channels-innermost DDF kernel takes the tensor as it is and
+            # applies BatchNorm + ReLU on its store
+            y = self.conv2.forward_channels_last(x, *self._bn2_scale_shift(x.device), relu=True)
+            if y is not None:
+                return torch.cudnn_convolution_add_relu(y, c3.weight, shortcut, 1.0, c3.bias, c3.stride,
+                                                        c3.padding, c3.dilation, 1)
+        x = self.conv2(x)  # DDFPack: contiguous NCHW out (or channels_last from its own NHWC path)
+        if x.is_contiguous(memory_format=torch.channels_last) and not x.is_contiguous():
+            x = self.act2(self.bn2(x))
+        elif shortcut.is_contiguous(memory_format=torch.channels_last) and not shortcut.is_contiguous():
             # channels_last network: BatchNorm + ReLU ride on the conversion back to NHWC
             x = to_channels_last(x, *self._bn2_scale_shift(x.device), relu=True)
         else:

@@ -119,6 +119,39 @@ int ddf_b200_forward_waitlimit(const void* x, const void* cf, const void* sf, vo
                                void* stream);
 
 /*
+ * Channels-innermost (NHWC, torch channels_last) forward.  The reference's op accepts
+ * contiguous NCHW only (CHECK_CONTIGUOUS, ddf/src/cuda/ddf_mul_cuda.cpp:28-32), so a
+ * network run with its --channels-last flag (train.py:369-370, 631-632) cannot reach it
+ * without layout copies; this entry point takes the tensors as such a network holds them.
+ *
+ *   x   (B,H,W,C)     cf (B,C,k,k)     out (B,H/s,W/s,C)
+ *   sf  k*k values per output pixel; the value of tap t at pixel (b,y,x) is read at element
+ *       b*sf_batch_stride + (y*(W/s) + x)*sf_pixel_stride + t*sf_tap_stride, which covers a
+ *       channels_last (B,G,H/s,W/s) tensor with G >= k*k maps (strides G*H'*W', G, 1) as well
+ *       as the reference's planar (B,k*k,H/s,W/s) layout (strides k*k*H'*W', 1, H'*W').
+ *   sf_bias (k*k floats or NULL) is added to the values read; with norm != 0 the spatial
+ *       FilterNorm of ddf_b200_forward_sfnorm is then applied in float (sf_scale as there).
+ *   out_scale / out_shift (C floats each, or both NULL) and relu: out = [relu](acc*scale+shift),
+ *       i.e. the eval-mode BatchNorm and activation that follow the DDFPack in the model.
+ * Built for k = 3, d = 1, s in {1, 2}, F16 / BF16, C a multiple of 8 that divides 2048;
+ * anything else returns DDF_B200_E_UNSUPPORTED and the caller converts to NCHW.  In add mode
+ * with norm != 0 the normalised filter is rounded to the element type before use, as the
+ * reference's module sequence does when it stores it.
+ *
+ * ddf_b200_pool_nhwc leaves the float partial sums of x over tiles of 196 pixels,
+ * partials (B, ddf_b200_pool_nhwc_tiles(H,W), C): the global average pool at the head of the
+ * channel branch (ddf/ddf.py:186), in the form ddf_b200_channel_filter takes.
+ */
+int ddf_b200_forward_nhwc(const void* x, const void* cf, const void* sf, const float* sf_bias,
+                          void* out, const float* out_scale, const float* out_shift, int relu,
+                          int B, int C, int H, int W, int k, int d, int s, int combine, int dtype,
+                          long long sf_batch_stride, long long sf_pixel_stride,
+                          long long sf_tap_stride, int norm, double sf_scale, void* stream);
+int ddf_b200_pool_nhwc_tiles(int H, int W);
+int ddf_b200_pool_nhwc(const void* x, float* partials, int B, int C, int H, int W, int dtype,
+                       void* stream);
+
+/*
  * Measurement aids (no counterpart in the reference, which measures with wall-clock loops,
  * test_time.py:11-51).  ddf_b200_noop enqueues an empty kernel: replayed from a CUDA graph
  * it gives the launch floor the small shapes are compared with.  ddf_b200_rate_probe
