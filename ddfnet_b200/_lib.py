@@ -26,6 +26,7 @@ SYMBOLS = (
     "ddf_b200_channel_filter", "ddf_b200_channel_filter_slice",
     "ddf_b200_frontend_tiles", "ddf_b200_pack_frontend", "ddf_b200_forward_waitlimit",
     "ddf_b200_forward_nhwc", "ddf_b200_pool_nhwc_tiles", "ddf_b200_pool_nhwc",
+    "ddf_b200_sfnorm", "ddf_b200_sfnorm_backward",
     "ddf_b200_noop", "ddf_b200_rate_probe_bytes", "ddf_b200_rate_probe",
 )
 
@@ -62,6 +63,10 @@ def load() -> ctypes.CDLL:
         L.ddf_b200_pool_nhwc_tiles.argtypes = [i, i]
         L.ddf_b200_pool_nhwc.restype = i
         L.ddf_b200_pool_nhwc.argtypes = [vp, vp] + [i] * 5 + [vp]
+        L.ddf_b200_sfnorm.restype = i
+        L.ddf_b200_sfnorm.argtypes = [vp, vp] + [i] * 5 + [ctypes.c_double, vp]
+        L.ddf_b200_sfnorm_backward.restype = i
+        L.ddf_b200_sfnorm_backward.argtypes = [vp, vp, vp] + [i] * 5 + [ctypes.c_double, vp]
         L.ddf_b200_noop.restype = i
         L.ddf_b200_noop.argtypes = [vp]
         L.ddf_b200_rate_probe_bytes.restype = sz

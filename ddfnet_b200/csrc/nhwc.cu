@@ -2,8 +2,7 @@
 // the pooled sums the channel branch needs, so that a channels_last network runs its DDF
 // layers without any layout copy.
 //
-// Mapping.  A thread owns 8 adjacent channels (one 16-byte vector) of PX adjacent output
-// pixels.  Its channel-filter values -- K*K taps x 8 channels, fixed for a sample -- sit in
+// Mapping.  A thread owns 8 adjacent channels (one 16-byte vector) of one output pixel column.  Its channel-filter values -- K*K taps x 8 channels, fixed for a sample -- sit in
 // registers as packed 2-byte pairs laid out like the input words (channels 2q, 2q+1 in word
 // q), so the mixed-precision FMA forms x * cf for both halves of a word without any
 // unpacking:  y = x * cf (exact in float),  acc = fma(y, sf, acc)  with the pixel's
@@ -11,7 +10,7 @@
 // pixel: every thread takes its pixels' K*K values (adding the convolution bias and applying
 // the spatial FilterNorm in float when asked to) once per pixel and reuses them for its 8
 // channels.  The threads of a pixel read C contiguous channels -- full 128-byte lines --
-// and the 3 x (PX + 2) window of a thread overlaps its neighbours', which the L1 cache
+// and the 3 x 3 window of a thread overlaps its neighbours', which the L1 cache
 // absorbs: there is no shared-memory staging and no barrier in this kernel.  Pixels outside
 // the image are not loaded (zeros take their place).  An optional per-channel affine map
 // and ReLU (an eval-mode BatchNorm + activation) ride on the store.
@@ -40,6 +39,7 @@ struct NhwcPlan {
     int vecs;               // C / 8
     int slots;              // strips a CTA works on = blockDim / vecs
     int strip_rows;         // output rows per strip
+    int sf_vector;          // the K*K values of a pixel are contiguous and 16-byte aligned
 };
 
 __device__ __forceinline__ uint4 ldg128(const void* p) {
@@ -62,8 +62,7 @@ constexpr int kNhwcThreads = 256;
 // two at stride 2) and keeps the others in registers; the loop is unrolled by three so that
 // the row rotation is register renaming, not moves.
 // NORM: `sf` holds the raw output of the spatial branch's convolution; bias and FilterNorm here.
-// SFV : the K*K values of a pixel are contiguous and 16-byte aligned (vector loads).
-template <typename T, int S, int PX, int MODE, bool NORM, bool SFV>
+template <typename T, int S, int PX, int MODE, bool NORM>
 __global__ void __launch_bounds__(kNhwcThreads, 2) nhwc_forward_kernel(const NhwcPlan pl) {
     constexpr int K = 3, KK = 9;
     constexpr int NCOL = (PX - 1) * S + 3;
@@ -123,6 +122,28 @@ __global__ void __launch_bounds__(kNhwcThreads, 2) nhwc_forward_kernel(const Nhw
         }
     };
 
+    // raw spatial-filter values of PX pixels as packed pairs (taps 2u, 2u+1)
+    auto load_sf = [&](const T* spp0, uint32_t (&raw)[PX][5]) {
+#pragma unroll
+        for (int px = 0; px < PX; ++px) {
+            const T* spp = spp0 + (long long)px * pl.sf_pixel_stride;
+            if (pl.sf_vector) {   // K*K contiguous values, 16-byte aligned
+                const uint4 u = ldg128(spp);
+                raw[px][0] = u.x; raw[px][1] = u.y; raw[px][2] = u.z; raw[px][3] = u.w;
+                raw[px][4] = __ldg(reinterpret_cast<const uint16_t*>(spp + 8));
+            } else {
+#pragma unroll
+                for (int u = 0; u < 5; ++u) {
+                    const uint32_t lo = __ldg(reinterpret_cast<const uint16_t*>(spp + (2 * u) * pl.sf_tap_stride));
+                    const uint32_t hi = 2 * u + 1 < KK ? __ldg(reinterpret_cast<const uint16_t*>(spp + (2 * u + 1) * pl.sf_tap_stride)) : 0u;
+                    raw[px][u] = lo | (hi << 16);
+                }
+            }
+        }
+    };
+    uint32_t sraw[PX][5];
+    load_sf(sp, sraw);
+
     uint32_t w0[NCOL][4], w1[NCOL][4], w2[NCOL][4];   // input rows oy*S - 1, oy*S, oy*S + 1
     load_row(oy0 * S - 1, w0);
     if constexpr (S == 1) load_row(oy0, w1);
@@ -131,22 +152,19 @@ __global__ void __launch_bounds__(kNhwcThreads, 2) nhwc_forward_kernel(const Nhw
     for (int oy = oy0; oy < oy1; ++oy) {
         if constexpr (S == 2) load_row(oy * 2, w1);
         load_row(oy * S + 1, w2);
-        // ---- the pixels' spatial-filter values in float (bias, FilterNorm)
+        // ---- the pixels' spatial-filter values in float (bias, FilterNorm); the raw values were
+        // requested one row ahead, and the next row's are requested now
         float sfv[PX][KK];
 #pragma unroll
         for (int px = 0; px < PX; ++px) {
-            const T* spp = sp + (long long)px * pl.sf_pixel_stride;
-            if constexpr (SFV) {
-                const uint4 u = ldg128(spp);
-                const uint32_t wv[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-                for (int t = 0; t < 8; ++t) sfv[px][t] = elem_to_float<T>((t & 1) ? (wv[t / 2] >> 16) : (wv[t / 2] & 0xffffu));
-                sfv[px][8] = elem_to_float<T>(__ldg(reinterpret_cast<const uint16_t*>(spp + 8)));
-            } else {
+            for (int t = 0; t < KK; ++t)
+                sfv[px][t] = elem_to_float<T>((t & 1) ? (sraw[px][t / 2] >> 16) : (sraw[px][t / 2] & 0xffffu));
+        }
+        sp += (long long)OW * pl.sf_pixel_stride;
+        if (oy + 1 < oy1) load_sf(sp, sraw);
 #pragma unroll
-                for (int t = 0; t < KK; ++t)
-                    sfv[px][t] = elem_to_float<T>(__ldg(reinterpret_cast<const uint16_t*>(spp + t * pl.sf_tap_stride)));
-            }
+        for (int px = 0; px < PX; ++px) {
             if constexpr (NORM) {
                 float sum = 0.f;
 #pragma unroll
@@ -211,16 +229,22 @@ __global__ void __launch_bounds__(kNhwcThreads, 2) nhwc_forward_kernel(const Nhw
         for (int px = 0; px < PX; ++px) {
             float r[8];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                r[c] = acc[px][c];
-                if (pl.oscale != nullptr) r[c] = fmaf(r[c], __ldg(pl.oscale + vec * 8 + c), __ldg(pl.oshift + vec * 8 + c));
-                if (pl.relu) r[c] = fmaxf(r[c], 0.f);
+            for (int c = 0; c < 8; ++c) r[c] = acc[px][c];
+            if (pl.oscale != nullptr) {
+                const float4* sc = reinterpret_cast<const float4*>(pl.oscale + vec * 8);
+                const float4* sh = reinterpret_cast<const float4*>(pl.oshift + vec * 8);
+                const float4 a0 = __ldg(sc), a1 = __ldg(sc + 1), b0 = __ldg(sh), b1 = __ldg(sh + 1);
+                r[0] = fmaf(r[0], a0.x, b0.x); r[1] = fmaf(r[1], a0.y, b0.y); r[2] = fmaf(r[2], a0.z, b0.z); r[3] = fmaf(r[3], a0.w, b0.w);
+                r[4] = fmaf(r[4], a1.x, b1.x); r[5] = fmaf(r[5], a1.y, b1.y); r[6] = fmaf(r[6], a1.z, b1.z); r[7] = fmaf(r[7], a1.w, b1.w);
+            }
+            if (pl.relu) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) r[c] = fmaxf(r[c], 0.f);
             }
             const uint4 o = make_uint4(pack2<T>(r[0], r[1]), pack2<T>(r[2], r[3]), pack2<T>(r[4], r[5]), pack2<T>(r[6], r[7]));
             *reinterpret_cast<uint4*>(op + (size_t)px * C) = o;
         }
         op += (size_t)OW * C;
-        sp += (long long)OW * pl.sf_pixel_stride;
         // rotate the rows: what was below becomes what is above
         if constexpr (S == 1) {
 #pragma unroll
@@ -268,27 +292,26 @@ __global__ void __launch_bounds__(256) nhwc_pool_kernel(const T* __restrict__ x,
     }
 }
 
-template <typename T, int S, int PX, bool SFV>
+template <typename T, int S, int PX>
 static int nhwc_launch(const NhwcPlan& pl, int combine, int norm, dim3 grid, cudaStream_t st) {
     if (combine == DDF_B200_MUL) {
-        if (norm) nhwc_forward_kernel<T, S, PX, DDF_B200_MUL, true, SFV><<<grid, kNhwcThreads, 0, st>>>(pl);
-        else nhwc_forward_kernel<T, S, PX, DDF_B200_MUL, false, SFV><<<grid, kNhwcThreads, 0, st>>>(pl);
+        if (norm) nhwc_forward_kernel<T, S, PX, DDF_B200_MUL, true><<<grid, kNhwcThreads, 0, st>>>(pl);
+        else nhwc_forward_kernel<T, S, PX, DDF_B200_MUL, false><<<grid, kNhwcThreads, 0, st>>>(pl);
     } else {
-        if (norm) nhwc_forward_kernel<T, S, PX, DDF_B200_ADD, true, SFV><<<grid, kNhwcThreads, 0, st>>>(pl);
-        else nhwc_forward_kernel<T, S, PX, DDF_B200_ADD, false, SFV><<<grid, kNhwcThreads, 0, st>>>(pl);
+        if (norm) nhwc_forward_kernel<T, S, PX, DDF_B200_ADD, true><<<grid, kNhwcThreads, 0, st>>>(pl);
+        else nhwc_forward_kernel<T, S, PX, DDF_B200_ADD, false><<<grid, kNhwcThreads, 0, st>>>(pl);
     }
     return (int)cudaGetLastError();
 }
 
+// One pixel column per thread: two columns would halve the window loads per output but need
+// 48 registers for the window alone, which does not fit beside the resident channel filter.
+constexpr int kNhwcPX = 1;
+
 template <typename T>
-static int nhwc_dispatch(const NhwcPlan& pl, int s, int combine, int norm, bool sfv, dim3 grid, cudaStream_t st) {
-    const bool pair = pl.OW % 2 == 0;
-#define DDF_NHWC(S_, PX_)                                                                    \
-    return sfv ? nhwc_launch<T, S_, PX_, true>(pl, combine, norm, grid, st)                  \
-               : nhwc_launch<T, S_, PX_, false>(pl, combine, norm, grid, st)
-    if (s == 1) { if (pair) { DDF_NHWC(1, 2); } else { DDF_NHWC(1, 1); } }
-    if (pair) { DDF_NHWC(2, 2); } else { DDF_NHWC(2, 1); }
-#undef DDF_NHWC
+static int nhwc_dispatch(const NhwcPlan& pl, int s, int combine, int norm, dim3 grid, cudaStream_t st) {
+    if (s == 1) return nhwc_launch<T, 1, kNhwcPX>(pl, combine, norm, grid, st);
+    return nhwc_launch<T, 2, kNhwcPX>(pl, combine, norm, grid, st);
 }
 
 }  // namespace ddf
@@ -353,8 +376,7 @@ int ddf_b200_forward_nhwc(const void* x, const void* cf, const void* sf, const f
     pl.slots = kNhwcThreads / pl.vecs;
     // Strips of output rows, PX columns wide: long enough that the two extra input rows a
     // strip reads are a small share, short enough that there are a few CTAs per SM.
-    const int px = pl.OW % 2 == 0 ? 2 : 1;
-    const int ppr = pl.OW / px;
+    const int ppr = pl.OW / kNhwcPX;
     int rows = pl.OH < 8 ? pl.OH : 8;
     auto n_ctas = [&](int r) { return (long long)B * (((long long)ppr * ((pl.OH + r - 1) / r) + pl.slots - 1) / pl.slots); };
     while (rows > 2 && n_ctas(rows) < 4ll * sm_count) rows = (rows + 1) / 2;
@@ -362,10 +384,10 @@ int ddf_b200_forward_nhwc(const void* x, const void* cf, const void* sf, const f
     const long long strips = (long long)ppr * ((pl.OH + rows - 1) / rows);
     dim3 grid((unsigned)((strips + pl.slots - 1) / pl.slots), (unsigned)B);
     // vector loads of the spatial filter: taps contiguous, pixels 16-byte aligned
-    const bool sfv = sf_tap_stride == 1 && sf_pixel_stride % 8 == 0 && sf_batch_stride % 8 == 0 && al16(sf);
+    pl.sf_vector = (sf_tap_stride == 1 && sf_pixel_stride % 8 == 0 && sf_batch_stride % 8 == 0 && al16(sf)) ? 1 : 0;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    rc = dtype == DDF_B200_F16 ? nhwc_dispatch<__half>(pl, s, combine, norm, sfv, grid, st)
-                               : nhwc_dispatch<__nv_bfloat16>(pl, s, combine, norm, sfv, grid, st);
+    rc = dtype == DDF_B200_F16 ? nhwc_dispatch<__half>(pl, s, combine, norm, grid, st)
+                               : nhwc_dispatch<__nv_bfloat16>(pl, s, combine, norm, grid, st);
     if (rc == 0) g_launches.fetch_add(1, std::memory_order_relaxed);
     return rc;
 }

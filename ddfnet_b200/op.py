@@ -119,8 +119,9 @@ class DDFSpatialNormFunction(Function):
     ``ddf_sfnorm(x, cf, raw, k, d, s, combine, scale, version)`` equals
     ``ddf(x, cf, FilterNorm_spatial(raw), k, d, s, combine, version)`` with the normalised
     filter never written to memory (it is kept in float inside the kernel).  The backward
-    recomputes the normalised filter with torch ops, runs the ordinary DDF backward on it
-    and passes the filter gradient back through the normalisation."""
+    recomputes the normalised filter with the library's ``ddf_b200_sfnorm``, runs the ordinary
+    DDF backward on it and carries the filter gradient back through the normalisation with
+    ``ddf_b200_sfnorm_backward``: no torch arithmetic on either path."""
 
     @staticmethod
     def forward(ctx, features, channel_filter, spatial_raw, kernel_size=3, dilation=1, stride=1,
@@ -155,15 +156,26 @@ class DDFSpatialNormFunction(Function):
     def backward(ctx, grad_output):
         features, channel_filter, spatial_raw = ctx.saved_tensors
         need_x, need_cf, need_sf = ctx.needs_input_grad[:3]
-        with torch.enable_grad():
-            raw = spatial_raw.detach().requires_grad_(need_sf)
-            normed = spatial_filter_norm(raw, ctx.kernel_size, ctx.scale)
-        gx, gcf, gsf = _backward_launch(ctx, grad_output, features, channel_filter,
-                                        normed.detach().to(features.dtype).contiguous(),
+        lib = _lib.load()
+        b, kk, oh, ow = spatial_raw.shape
+        dtc = _DTYPES[spatial_raw.dtype]
+        # the normalised filter, recomputed once by the library for the gradient kernels
+        normed = torch.empty_like(spatial_raw)
+        with torch.cuda.device(features.device):
+            stream = torch.cuda.current_stream().cuda_stream
+            _lib.check(lib.ddf_b200_sfnorm(spatial_raw.data_ptr(), normed.data_ptr(), b, ctx.kernel_size, oh, ow,
+                                           dtc, ctx.scale, stream))
+        gx, gcf, gsf = _backward_launch(ctx, grad_output, features, channel_filter, normed,
                                         (need_x, need_cf, need_sf))
         graw = None
         if need_sf:
-            (graw,) = torch.autograd.grad(normed, raw, gsf.to(normed.dtype))
+            # ... and the filter gradient carried back through the normalisation
+            graw = torch.empty_like(spatial_raw)
+            gsf = gsf.contiguous()
+            with torch.cuda.device(features.device):
+                _lib.check(lib.ddf_b200_sfnorm_backward(
+                    spatial_raw.data_ptr(), gsf.data_ptr(), graw.data_ptr(), b, ctx.kernel_size, oh, ow, dtc,
+                    ctx.scale, torch.cuda.current_stream().cuda_stream))
         dx, dcf, dsf = ctx.in_dtypes
         gx = gx.to(dx) if gx is not None else None
         gcf = gcf.to(dcf) if gcf is not None else None

@@ -119,6 +119,20 @@ int ddf_b200_forward_waitlimit(const void* x, const void* cf, const void* sf, vo
                                void* stream);
 
 /*
+ * The spatial FilterNorm on its own, for the backward of ddf_b200_forward_sfnorm.
+ * ddf_b200_sfnorm writes the normalised filter (same shape and type as `raw`,
+ * (B,k*k,H',W')) that ddf_b200_backward takes as `sf`; ddf_b200_sfnorm_backward turns the
+ * gradient with respect to the normalised filter (ddf_b200_backward's gsf) into the
+ * gradient with respect to the raw filter.  Replace FilterNorm(filter_type='spatial').forward
+ * (ddf/ddf.py:146-157) and the autograd of those torch operations.  Statistics in float
+ * (double for F64).  k in {3, 5, 7}.
+ */
+int ddf_b200_sfnorm(const void* raw, void* normed, int B, int k, int OH, int OW, int dtype,
+                    double sf_scale, void* stream);
+int ddf_b200_sfnorm_backward(const void* raw, const void* grad_normed, void* grad_raw,
+                             int B, int k, int OH, int OW, int dtype, double sf_scale, void* stream);
+
+/*
  * Channels-innermost (NHWC, torch channels_last) forward.  The reference's op accepts
  * contiguous NCHW only (CHECK_CONTIGUOUS, ddf/src/cuda/ddf_mul_cuda.cpp:28-32), so a
  * network run with its --channels-last flag (train.py:369-370, 631-632) cannot reach it

@@ -107,21 +107,63 @@ def test_fused_gradcheck_float64(comb):
                                     (x, cf, raw), eps=1e-3, atol=1e-5)
 
 
-@pytest.mark.parametrize("dt", ["f32", "bf16"])
-def test_fused_backward_matches_unfused_chain(dt):
-    """Gradients of the fused op against autograd through torch FilterNorm ops + the plain op."""
-    from ddfnet_b200 import ddf, ddf_sfnorm
-    from ddfnet_b200.op import spatial_filter_norm
+@pytest.mark.parametrize("dt", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("comb", ["mul", "add"])
+def test_fused_backward_matches_oracle(dt, comb):
+    """Gradients of the fused op (recomputed filter by ddf_b200_sfnorm, DDF backward, norm
+    Jacobian by ddf_b200_sfnorm_backward) against the float64 oracle: the CPU oracle's DDF
+    gradients on the float64-normalised filter, carried through a float64 autograd of the
+    normalisation written out from its definition (ddf/ddf.py:146-152)."""
+    from ddfnet_b200 import ddf_sfnorm
+    from oracle import ddf_oracle
     dtype = DTYPES[dt]
     dev = torch.device("cuda:0")
-    x, cf, raw = (t.to(dev) for t in _inputs(8, 128, 28, 28, 3, 1, dtype, 21))
-    go = torch.randn(8, 128, 28, 28, device=dev).to(dtype)
-    a = [t.clone().requires_grad_() for t in (x, cf, raw)]
-    ddf_sfnorm(a[0], a[1], a[2], 3, 1, 1, "mul", SCALE).backward(go)
-    b = [t.clone().requires_grad_() for t in (x, cf, raw)]
-    ddf(b[0], b[1], spatial_filter_norm(b[2], 3, SCALE).to(dtype), 3, 1, 1, "mul").backward(go)
-    tol = 1e-4 if dtype == torch.float32 else 3e-2
-    for name, p, q in zip(("gx", "gcf", "graw"), a, b):
-        num = (p.grad.double() - q.grad.double()).norm().item()
-        den = q.grad.double().norm().item()
-        assert num <= tol * den, (name, num / den)
+    B, C, H = 4, 48, 14
+    x, cf, raw = _inputs(B, C, H, H, 3, 1, dtype, 21)
+    go = torch.randn(B, C, H, H, generator=torch.Generator().manual_seed(5)).to(dtype)
+    a = [t.to(dev).requires_grad_() for t in (x, cf, raw)]
+    ddf_sfnorm(a[0], a[1], a[2], 3, 1, 1, comb, SCALE).backward(go.to(dev))
+    v = raw.double().requires_grad_()
+    c = v - v.mean(dim=1, keepdim=True)
+    normed = c / ((c * c).sum(dim=1, keepdim=True) / 8).sqrt().add(1e-10) * SCALE
+    assert torch.allclose(normed.detach(), ddf_oracle.filter_norm_spatial(raw.double(), 1, 3, SCALE), atol=1e-12)
+    gx, gcf, gsf = ddf_oracle.backward(go.double(), x.double(), cf.double(), normed.detach(), 3, 1, 1, comb)
+    (graw,) = torch.autograd.grad(normed, v, gsf)
+    # float32: the project's 1e-5 bound.  2-byte types: the backward stores the recomputed filter
+    # and the filter gradient in the element type (as the unfused module sequence does), so the
+    # aggregate bound is that type's rounding: relative L2 of 2**-9 (f16: 2**-11) times a small factor.
+    for name, got, want in zip(("gx", "gcf", "graw"), (a[0].grad, a[1].grad, a[2].grad), (gx, gcf, graw)):
+        if dtype == torch.float32:
+            check_close(got, want, dtype, f"fused backward {name} {comb}", reduction=name != "gx")
+        else:
+            rel = ((got.double().cpu() - want).norm() / want.norm()).item()
+            assert rel <= (6e-3 if dtype == torch.bfloat16 else 1e-3), (name, rel)
+
+
+def test_sfnorm_kernels_float64():
+    """ddf_b200_sfnorm / ddf_b200_sfnorm_backward in float64 against autograd, k = 3 and 5, including
+    a pixel whose values are all equal (zero spread: the gradient of the spread term is dropped)."""
+    from ddfnet_b200 import _lib
+    L = _lib.load()
+    dev = torch.device("cuda:0")
+    for k in (3, 5):
+        kk = k * k
+        g = torch.Generator().manual_seed(k)
+        raw = torch.randn(3, kk, 6, 5, generator=g, dtype=torch.float64)
+        raw[0, :, 0, 0] = 0.25
+        gy = torch.randn(3, kk, 6, 5, generator=g, dtype=torch.float64)
+        rd, gd = raw.to(dev), gy.to(dev)
+        out, gr = torch.empty_like(rd), torch.empty_like(rd)
+        assert L.ddf_b200_sfnorm(rd.data_ptr(), out.data_ptr(), 3, k, 6, 5, _lib.F64, 0.4, None) == 0
+        assert L.ddf_b200_sfnorm_backward(rd.data_ptr(), gd.data_ptr(), gr.data_ptr(), 3, k, 6, 5, _lib.F64, 0.4, None) == 0
+        torch.cuda.synchronize()
+        v = raw.clone().requires_grad_()
+        c = v - v.mean(dim=1, keepdim=True)
+        y = c / ((c * c).sum(dim=1, keepdim=True) / (kk - 1)).sqrt().add(1e-10) * 0.4
+        mask = torch.ones(3, 1, 6, 5, dtype=torch.bool)
+        mask[0, 0, 0, 0] = False
+        (want,) = torch.autograd.grad(y, v, gy * mask)
+        assert torch.allclose(out.cpu(), y.detach(), atol=1e-12)
+        keep = mask.expand_as(want)
+        assert torch.allclose(gr.cpu()[keep], want[keep], atol=1e-10)
+        assert torch.isfinite(gr).all()
