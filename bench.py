@@ -61,12 +61,12 @@ def peaks():
     return 6650.0, "fallback"
 
 
-def make_case(C, H, s, dtype, B, device, seed):
+def make_case(C, H, s, dtype, B, device, seed, k=K):
     g = torch.Generator().manual_seed(seed)
     oh = H // s
     x = torch.randn(B, C, H, H, generator=g).relu_().to(dtype)
-    cf = (torch.randn(B, C, K, K, generator=g) / 3).to(dtype)
-    sf = (torch.randn(B, K * K, oh, oh, generator=g) / 3).to(dtype)
+    cf = (torch.randn(B, C, k, k, generator=g) / 3).to(dtype)
+    sf = (torch.randn(B, k * k, oh, oh, generator=g) / 3).to(dtype)
     if device is None:
         return x, cf, sf
     return x.to(device), cf.to(device), sf.to(device)
@@ -734,24 +734,40 @@ def run_probe(args, rank, world, local_rank):
 
 
 def run_ncu_case(spec):
+    """C,H,stride,dtype,combine followed by any of: backward, nhwc, k=5, d=2."""
     from ddfnet_b200 import ddf
     parts = spec.split(",")
     C, H, s = int(parts[0]), int(parts[1]), int(parts[2])
     dtype = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[parts[3]]
     mode = parts[4]
-    backward = len(parts) > 5 and parts[5] == "backward"
+    flags = parts[5:]
+    backward, nhwc = "backward" in flags, "nhwc" in flags
+    k = next((int(f[2:]) for f in flags if f.startswith("k=")), K)
+    d = next((int(f[2:]) for f in flags if f.startswith("d=")), D)
     dev = torch.device("cuda:0")
     B = 64 if backward else BATCH
-    sets = [make_case(C, H, s, dtype, B, dev, 7 + i) for i in range(3)]
+    sets = [make_case(C, H, s, dtype, B, dev, 7 + i, k=k) for i in range(3)]
     if backward:
         go = torch.randn(B, C, H // s, H // s, device=dev).to(dtype)
         for i in range(6):
             xs = [t.detach().requires_grad_() for t in sets[i % 3]]
-            ddf(*xs, K, D, s, mode).backward(go)
+            ddf(*xs, k, d, s, mode).backward(go)
+    elif nhwc:
+        # channels_last input and spatial filter (the filter's tap axis padded to 16, as the
+        # spatial branch's convolution produces it): the layout-native kernel
+        from ddfnet_b200.nhwc import ddf_nhwc
+        cl = []
+        for x, cf, sf in sets:
+            sf16 = torch.zeros(sf.shape[0], 16, sf.shape[2], sf.shape[3], dtype=sf.dtype, device=dev)
+            sf16[:, :k * k] = sf
+            cl.append((x.contiguous(memory_format=torch.channels_last), cf,
+                       sf16.contiguous(memory_format=torch.channels_last)))
+        for i in range(6):
+            ddf_nhwc(*cl[i % 3], k, d, s, mode)
     else:
         with torch.no_grad():
             for i in range(6):
-                ddf(*sets[i % 3], K, D, s, mode)
+                ddf(*sets[i % 3], k, d, s, mode)
     torch.cuda.synchronize()
     print("ok")
 
@@ -820,7 +836,7 @@ def main():
                     help="model workload: fold every BatchNorm that follows a convolution into it; "
                          "'fused' also uses cuDNN's fused conv+bias(+add)+ReLU calls")
     ap.add_argument("--detail", default=None, help="also write the JSON, indented, to this file")
-    ap.add_argument("--ncu-case", default=None, metavar="C,H,stride,dtype,combine[,backward]",
+    ap.add_argument("--ncu-case", default=None, metavar="C,H,stride,dtype,combine[,backward][,nhwc][,k=5][,d=2]",
                     help="profiling aid: run only this case, 6 launches over 3 rotating buffer "
                          "sets at B=128 (B=64 for backward), print nothing but 'ok'")
     args = ap.parse_args()
