@@ -84,7 +84,7 @@ def load() -> ctypes.CDLL:
         L.ddf_b200_frontend_tiles.restype = i
         L.ddf_b200_frontend_tiles.argtypes = [i, i]
         L.ddf_b200_pack_frontend.restype = i
-        L.ddf_b200_pack_frontend.argtypes = [vp] * 6 + [i] * 7 + [vp]
+        L.ddf_b200_pack_frontend.argtypes = [vp] * 3 + [i] * 5 + [vp]
         L.ddf_b200_channel_filter_slice.restype = i
         L.ddf_b200_channel_filter_slice.argtypes = [i]
         L.ddf_b200_channel_filter.restype = i

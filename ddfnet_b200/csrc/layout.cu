@@ -201,29 +201,22 @@ int ddf_b200_nchw_to_nhwc(const void* src, void* dst, int B, int C, int H, int W
 // ---------------------------------------------------------------------------------------
 // Front end of a DDF layer in a channels-last network, one pass over x (B,H,W,C):
 //   x_nchw (B,C,H,W)          the op's input (the transpose above),
-//   raw    (B,G,H/s,W/s)      the spatial branch's 1x1 convolution with stride s and bias
-//                             (G = head*k*k maps; build_spatial_branch, ddf/ddf.py:176-180),
 //   pooled (B,NT,C) float     per-channel sums over each 64-pixel tile: the global average
 //                             pool of the channel branch (ddf/ddf.py:187) as partial sums
 //                             that ddf_b200_channel_filter adds in a fixed order.
-// The reference reads x once for each of these (and the op a fourth time); here the tile
-// that is being transposed through shared memory also feeds the convolution and the sums.
+// The reference reads x once for each of these; here the tile that is being transposed
+// through shared memory also feeds the sums.  (The spatial branch's 1x1 convolution is left
+// to the tensor-core library: computed here on CUDA cores it cost more than it saved.)
 namespace ddf {
 
-constexpr int kFeMaxG = 36;    // head * k * k <= 36: at most nine maps per thread
 constexpr int kFeMaxC = 2048;
-constexpr size_t kFeMaxWeightBytes = 160 * 1024;  // the convolution weight sits in shared memory as float
 
-// CONV = false: no convolution; the channel tiles then spread over gridDim.z instead of a
-// loop, as in the plain transpose.
-template <typename T, bool CONV>
+template <typename T>
 __global__ void __launch_bounds__(256)
-frontend_kernel(const T* __restrict__ x, T* __restrict__ x_nchw, const T* __restrict__ ws,
-                const T* __restrict__ bs, T* __restrict__ raw, float* __restrict__ pooled,
-                int C, int H, int W, int G, int stride) {
+frontend_kernel(const T* __restrict__ x, T* __restrict__ x_nchw, float* __restrict__ pooled,
+                int C, int H, int W) {
     constexpr int PITCH = kTile + (sizeof(T) == 2 ? 2 : 1);
     __shared__ T tile[kTile][PITCH];  // [channel][pixel]
-    extern __shared__ __align__(16) float wsm[];  // [G][C]
     const int t = threadIdx.x;
     const int HW = H * W;
     const int p0 = blockIdx.x * kTile;
@@ -232,121 +225,55 @@ frontend_kernel(const T* __restrict__ x, T* __restrict__ x_nchw, const T* __rest
     T* d = x_nchw + b * (long long)C * HW;
     const int sub = t >> 4, q = (t & 15) * 4;
     const bool vec_hw = (HW % 4) == 0, vec_c = (C % 4) == 0;
-
-    if (CONV) {
-        for (int i = t; i < G * C; i += 256) wsm[i] = (float)ws[i];
-    }
-
-    // convolution: thread = (pixel of the tile, group of maps g = grp, grp + 4, ...)
-    const int cp = t & 63, grp = t >> 6;
-    float acc[kFeMaxG / 4];
-#pragma unroll
-    for (int j = 0; j < kFeMaxG / 4; ++j) acc[j] = 0.f;
     // pooled sums: thread = (channel of the tile, quarter of its pixels)
     const int pc = t >> 2, pq = t & 3;
+    const int c0 = (int)blockIdx.z * kTile;
 
-    const int c_begin = CONV ? 0 : (int)blockIdx.z * kTile;
-    const int c_end = CONV ? C : (c_begin + kTile < C ? c_begin + kTile : C);
-    for (int c0 = c_begin; c0 < c_end; c0 += kTile) {
-        __syncthreads();  // previous tile fully consumed (and wsm written, first time round)
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int p = p0 + r * 16 + sub, c = c0 + q;
+    for (int r = 0; r < 4; ++r) {
+        const int p = p0 + r * 16 + sub, c = c0 + q;
+        T v[4];
+        if (p < HW && c < C) {
+            load4(s + (long long)p * C + c, vec_c, C - c < 4 ? C - c : 4, v);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] = T(0.f);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) tile[q + i][r * 16 + sub] = v[i];
+    }
+    __syncthreads();
+    // (1) transpose out
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int c = c0 + r * 16 + sub, p = p0 + q;
+        if (c < C && p < HW) {
             T v[4];
-            if (p < HW && c < C) {
-                load4(s + (long long)p * C + c, vec_c, C - c < 4 ? C - c : 4, v);
-            } else {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) v[i] = T(0.f);
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) tile[q + i][r * 16 + sub] = v[i];
-        }
-        __syncthreads();
-        // (1) transpose out
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-            const int c = c0 + r * 16 + sub, p = p0 + q;
-            if (c < C && p < HW) {
-                T v[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) v[i] = tile[r * 16 + sub][q + i];
-                store4(d + (long long)c * HW + p, vec_hw, HW - p < 4 ? HW - p : 4, v);
-            }
-        }
-        // (2) per-channel sums over the tile's pixels (out-of-range entries are zero)
-        {
-            float sum = 0.f;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) sum += (float)tile[pc][pq * 16 + i];
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            if (pq == 0 && c0 + pc < C)
-                pooled[(b * gridDim.x + blockIdx.x) * (long long)C + c0 + pc] = sum;
-        }
-        // (3) 1x1 convolution: this pixel, this thread's maps, the tile's channels
-        if (CONV) {
-            const int cn = (C - c0) < kTile ? (C - c0) : kTile;
-            for (int cc = 0; cc < cn; ++cc) {
-                const float xv = (float)tile[cc][cp];
-#pragma unroll
-                for (int j = 0; j < kFeMaxG / 4; ++j) {
-                    const int gi = grp + 4 * j;
-                    if (gi < G) acc[j] = fmaf(xv, wsm[gi * C + c0 + cc], acc[j]);
-                }
-            }
+            for (int i = 0; i < 4; ++i) v[i] = tile[r * 16 + sub][q + i];
+            store4(d + (long long)c * HW + p, vec_hw, HW - p < 4 ? HW - p : 4, v);
         }
     }
-    // write the maps of the pixels that survive the stride
-    const int p = p0 + cp;
-    if (CONV && p < HW) {
-        const int y = p / W, xx = p - y * W;
-        const int OH = H / stride, OW = W / stride;
-        if (y % stride == 0 && xx % stride == 0 && y / stride < OH && xx / stride < OW) {
-            const long long op = (long long)(y / stride) * OW + xx / stride;
+    // (2) per-channel sums over the tile's pixels (out-of-range entries are zero)
+    float sum = 0.f;
 #pragma unroll
-            for (int j = 0; j < kFeMaxG / 4; ++j) {
-                const int gi = grp + 4 * j;
-                if (gi < G)
-                    raw[(b * G + gi) * (long long)OH * OW + op] = (T)(acc[j] + (float)bs[gi]);
-            }
-        }
-    }
+    for (int i = 0; i < 16; ++i) sum += (float)tile[pc][pq * 16 + i];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (pq == 0 && c0 + pc < C)
+        pooled[(b * gridDim.x + blockIdx.x) * (long long)C + c0 + pc] = sum;
 }
 
 template <typename T>
-static int frontend_launch(const void* x, void* x_nchw, const void* ws, const void* bs, void* raw,
-                           float* pooled, int B, int C, int H, int W, int G, int stride,
+static int frontend_launch(const void* x, void* x_nchw, float* pooled, int B, int C, int H, int W,
                            cudaStream_t st) {
     const uintptr_t mask = sizeof(T) * 4 - 1;
     if ((reinterpret_cast<uintptr_t>(x) & mask) || (reinterpret_cast<uintptr_t>(x_nchw) & mask))
         return DDF_B200_E_UNSUPPORTED;
     const int HW = H * W;
-    dim3 grid((unsigned)((HW + kTile - 1) / kTile), (unsigned)B, 1u);
+    dim3 grid((unsigned)((HW + kTile - 1) / kTile), (unsigned)B, (unsigned)((C + kTile - 1) / kTile));
     if (grid.y > 65535u) return DDF_B200_E_TOO_LARGE;
-    if (G == 0) {
-        grid.z = (unsigned)((C + kTile - 1) / kTile);
-        frontend_kernel<T, false><<<grid, 256, 0, st>>>((const T*)x, (T*)x_nchw, nullptr, nullptr, nullptr,
-                                                       pooled, C, H, W, 0, stride);
-        g_launches.fetch_add(1, std::memory_order_relaxed);
-        return (int)cudaGetLastError();
-    }
-    const size_t smem = sizeof(float) * (size_t)G * C;
-    auto kern = frontend_kernel<T, true>;
-    if (smem > kFeMaxWeightBytes) return DDF_B200_E_UNSUPPORTED;
-    // static tile + dynamic weights may pass the 48 KB default: opt in once per device
-    static std::atomic<unsigned long long> opted{0};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return (int)e;
-    const unsigned long long bit = 1ull << (dev & 63);
-    if (!(opted.load(std::memory_order_acquire) & bit)) {
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFeMaxWeightBytes);
-        if (e != cudaSuccess) return (int)e;
-        opted.fetch_or(bit, std::memory_order_release);
-    }
-    kern<<<grid, 256, smem, st>>>((const T*)x, (T*)x_nchw, (const T*)ws, (const T*)bs, (T*)raw, pooled,
-                                  C, H, W, G, stride);
+    frontend_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (T*)x_nchw, pooled, C, H, W);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return (int)cudaGetLastError();
 }
@@ -355,23 +282,17 @@ static int frontend_launch(const void* x, void* x_nchw, const void* ws, const vo
 
 extern "C" int ddf_b200_frontend_tiles(int H, int W) { return (H * W + ddf::kTile - 1) / ddf::kTile; }
 
-extern "C" int ddf_b200_pack_frontend(const void* x_nhwc, void* x_nchw, const void* w_spatial,
-                                      const void* b_spatial, void* raw, float* pooled, int B, int C,
-                                      int H, int W, int G, int stride, int dtype, void* stream) {
+extern "C" int ddf_b200_pack_frontend(const void* x_nhwc, void* x_nchw, float* pooled, int B, int C,
+                                      int H, int W, int dtype, void* stream) {
     using namespace ddf;
     if (!x_nhwc || !x_nchw || !pooled) return DDF_B200_E_NULL;
-    if (G > 0 && (!w_spatial || !b_spatial || !raw)) return DDF_B200_E_NULL;
-    if (B < 1 || C < 1 || H < 1 || W < 1 || G < 0 || stride < 1 || H / stride < 1 || W / stride < 1)
-        return DDF_B200_E_SHAPE;
-    if (G > kFeMaxG || C > kFeMaxC || (long long)H * W > (1ll << 30)) return DDF_B200_E_UNSUPPORTED;
+    if (B < 1 || C < 1 || H < 1 || W < 1) return DDF_B200_E_SHAPE;
+    if (C > kFeMaxC || (long long)H * W > (1ll << 30)) return DDF_B200_E_UNSUPPORTED;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     switch (dtype) {
-        case DDF_B200_F32:
-            return frontend_launch<float>(x_nhwc, x_nchw, w_spatial, b_spatial, raw, pooled, B, C, H, W, G, stride, st);
-        case DDF_B200_F16:
-            return frontend_launch<__half>(x_nhwc, x_nchw, w_spatial, b_spatial, raw, pooled, B, C, H, W, G, stride, st);
-        case DDF_B200_BF16:
-            return frontend_launch<__nv_bfloat16>(x_nhwc, x_nchw, w_spatial, b_spatial, raw, pooled, B, C, H, W, G, stride, st);
+        case DDF_B200_F32: return frontend_launch<float>(x_nhwc, x_nchw, pooled, B, C, H, W, st);
+        case DDF_B200_F16: return frontend_launch<__half>(x_nhwc, x_nchw, pooled, B, C, H, W, st);
+        case DDF_B200_BF16: return frontend_launch<__nv_bfloat16>(x_nhwc, x_nchw, pooled, B, C, H, W, st);
         default: return DDF_B200_E_DTYPE;
     }
 }

@@ -90,41 +90,27 @@ def build_channel_branch(in_channels, kernel_size, nonlinearity='relu', se_ratio
         FilterNorm(in_channels, kernel_size, 'channel', nonlinearity, running_std=True))
 
 
-def pack_frontend(x: torch.Tensor, conv: nn.Conv2d | None = None):
+def pack_frontend(x: torch.Tensor):
     """One pass over a channels_last ``x`` through ``ddf_b200_pack_frontend``: (x as contiguous
-    NCHW, the 1x1 convolution ``conv`` of x as contiguous NCHW or None when ``conv`` is None,
-    per-tile channel sums (B, NT, C) float32).  Returns None when the case is outside the
+    NCHW, per-tile channel sums (B, NT, C) float32).  Returns None when the case is outside the
     kernel's range or gradients are being recorded."""
     from . import _lib
     from .op import _DTYPES
-    if torch.is_grad_enabled() and (x.requires_grad or (conv is not None and conv.weight.requires_grad)):
+    if torch.is_grad_enabled() and x.requires_grad:
         return None
     b, c, h, w = x.shape
     if (not x.is_cuda or x.dtype not in _DTYPES or x.dtype == torch.float64 or x.is_contiguous()
             or not x.is_contiguous(memory_format=torch.channels_last) or c > 2048):
         return None
-    g, s = 0, 1
-    if conv is not None:
-        g, s = conv.out_channels, conv.stride[0]
-        if (conv.kernel_size != (1, 1) or conv.stride[0] != conv.stride[1] or conv.bias is None
-                or conv.weight.dtype != x.dtype or g > 36 or g * c * 4 > 160 * 1024
-                or h % s != 0 or w % s != 0):
-            return None
     lib = _lib.load()
     nt = int(lib.ddf_b200_frontend_tiles(h, w))
     x_nchw = torch.empty((b, c, h, w), dtype=x.dtype, device=x.device)
     pooled = torch.empty((b, nt, c), dtype=torch.float32, device=x.device)
-    raw = wsp = None
-    if conv is not None:
-        raw = torch.empty((b, g, h // s, w // s), dtype=x.dtype, device=x.device)
-        wsp = conv.weight.detach().reshape(g, c).contiguous()
-    ptr = lambda t: t.data_ptr() if t is not None else None
     with torch.cuda.device(x.device):
         _lib.check(lib.ddf_b200_pack_frontend(
-            x.data_ptr(), x_nchw.data_ptr(), ptr(wsp), ptr(conv.bias if conv is not None else None),
-            ptr(raw), pooled.data_ptr(), b, c, h, w, g, s, _DTYPES[x.dtype],
+            x.data_ptr(), x_nchw.data_ptr(), pooled.data_ptr(), b, c, h, w, _DTYPES[x.dtype],
             torch.cuda.current_stream().cuda_stream))
-    return x_nchw, raw, pooled
+    return x_nchw, pooled
 
 
 def _padded_spatial_conv(conv: nn.Conv2d):
@@ -282,7 +268,7 @@ class DDFPack(nn.Module):
         channel_filter = None
         if self.fuse_channel_branch:
             channel_filter = channel_filter_fused(self.channel_branch, x_in, k,
-                                                  front[2] if front is not None else None)
+                                                  front[1] if front is not None else None)
         if channel_filter is None:
             channel_filter = self.channel_branch(x_in)
         channel_filter = channel_filter.reshape(b * g, c // g, k, k).contiguous()

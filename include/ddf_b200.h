@@ -274,31 +274,20 @@ int ddf_b200_nhwc_to_nchw_affine(const void* src, void* dst, int B, int C, int H
 
 /*
  * Front end of a DDF layer in a channels-last network: ONE pass over x (B,H,W,C)
- * produces the op's NCHW input, the spatial branch's raw filter and the channel
- * branch's pooled sums.
+ * produces the op's NCHW input and the channel branch's pooled sums.
  *   x_nchw (B,C,H,W)        x transposed (as ddf_b200_nhwc_to_nchw)
- *   raw    (B,G,H/s,W/s)    1x1 convolution of x with stride s: w_spatial (G,C),
- *                           b_spatial (G), G = head*k*k <= 36 -- the convolution of
- *                           build_spatial_branch (ddf/ddf.py:176-180); feed it to
- *                           ddf_b200_forward_sfnorm
  *   pooled (B,NT,C) float   per-channel sums of x over each of the
  *                           NT = ddf_b200_frontend_tiles(H,W) 64-pixel tiles -- the
  *                           AdaptiveAvgPool2d of build_channel_branch (ddf/ddf.py:187)
  *                           as partial sums; feed them to ddf_b200_channel_filter with
  *                           n_partials = NT, pool_scale = 1/(H*W)
- * G = 0 skips the convolution (w_spatial, b_spatial, raw may then be NULL).  The
- * convolution runs on the CUDA cores (nine multiply-adds per element) and is slower
- * than the library's tensor-core convolution (198 us against about 120 us per layer of
- * ddf_mul_resnet50 at batch 256): the Python DDFPack calls this with G = 0 and keeps the
- * library convolution.
  * The reference reads x once for each of these.  Inference path (no gradients);
- * dtype F32 / F16 / BF16; C <= 2048 and G*C*4 bytes <= 160 KB; x_nhwc and x_nchw
- * 16-byte aligned (DDF_B200_E_UNSUPPORTED otherwise).
+ * dtype F32 / F16 / BF16; C <= 2048; x_nhwc and x_nchw 16-byte aligned
+ * (DDF_B200_E_UNSUPPORTED otherwise).
  */
 int ddf_b200_frontend_tiles(int H, int W);
-int ddf_b200_pack_frontend(const void* x_nhwc, void* x_nchw, const void* w_spatial,
-                           const void* b_spatial, void* raw, float* pooled,
-                           int B, int C, int H, int W, int G, int stride, int dtype, void* stream);
+int ddf_b200_pack_frontend(const void* x_nhwc, void* x_nchw, float* pooled, int B, int C, int H,
+                           int W, int dtype, void* stream);
 
 /*
  * The channel branch of a DDF layer after its global average pool, as one launch:

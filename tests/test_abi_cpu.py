@@ -82,10 +82,10 @@ def test_argument_checks_of_the_adjacent_entry_points(L):
     assert L.ddf_b200_nhwc_to_nchw(ctypes.c_void_p(4098), fake, 1, 4, 8, 8, 1, None) == -7  # misaligned
     # front end
     assert L.ddf_b200_frontend_tiles(56, 56) == 49 and L.ddf_b200_frontend_tiles(7, 7) == 1
-    assert L.ddf_b200_pack_frontend(None, None, None, None, None, None, 1, 4, 8, 8, 0, 1, 0, None) == -1
-    assert L.ddf_b200_pack_frontend(fake, fake, None, None, None, fake, 1, 4, 8, 8, 9, 1, 0, None) == -1
-    assert L.ddf_b200_pack_frontend(fake, fake, fake, fake, fake, fake, 1, 4, 8, 8, 40, 1, 0, None) == -7
-    assert L.ddf_b200_pack_frontend(fake, fake, None, None, None, fake, 1, 4, 8, 8, 0, 1, 3, None) == -5
+    assert L.ddf_b200_pack_frontend(None, None, None, 1, 4, 8, 8, 0, None) == -1
+    assert L.ddf_b200_pack_frontend(fake, fake, fake, 1, 0, 8, 8, 0, None) == -2
+    assert L.ddf_b200_pack_frontend(fake, fake, fake, 1, 4096, 8, 8, 0, None) == -7
+    assert L.ddf_b200_pack_frontend(fake, fake, fake, 1, 4, 8, 8, 3, None) == -5
     # channel branch
     cf = lambda *a: L.ddf_b200_channel_filter(fake, 1, 1.0, fake, fake, fake, fake, fake, fake, *a, None)
     assert L.ddf_b200_channel_filter(None, 1, 1.0, fake, fake, fake, fake, fake, fake, 1, 64, 12, 3, 0, None) == -1

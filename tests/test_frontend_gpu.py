@@ -1,16 +1,14 @@
-"""ddf_b200_pack_frontend (one pass over a channels_last x: NCHW copy, spatial 1x1 convolution,
-pooled partial sums) against plain torch arithmetic in float64 on the same rounded values."""
+"""ddf_b200_pack_frontend (one pass over a channels_last x: NCHW copy and pooled partial sums)
+against plain torch arithmetic in float64 on the same rounded values."""
 import pytest
 import torch
-import torch.nn as nn
 
 from tests.util import DTYPES
 
 pytestmark = pytest.mark.gpu
 
-CASES = [  # B, C, H, W, G, stride
-    (2, 64, 56, 56, 9, 1), (2, 128, 28, 28, 9, 2), (3, 256, 14, 14, 9, 1), (2, 512, 7, 7, 9, 1),
-    (2, 64, 28, 28, 18, 1), (1, 72, 10, 12, 9, 2), (2, 128, 56, 56, 9, 2),
+CASES = [  # B, C, H, W
+    (2, 64, 56, 56), (2, 128, 28, 28), (3, 256, 14, 14), (2, 512, 7, 7), (1, 72, 10, 12), (2, 128, 56, 56),
 ]
 
 
@@ -18,24 +16,17 @@ CASES = [  # B, C, H, W, G, stride
 @pytest.mark.parametrize("case", CASES)
 def test_frontend_matches_torch(case, dt):
     from ddfnet_b200.modules import pack_frontend
-    B, C, H, W, G, s = case
+    B, C, H, W = case
     dtype = DTYPES[dt]
     dev = torch.device("cuda:0")
-    torch.manual_seed(C + H + G)
-    conv = nn.Conv2d(C, G, 1, stride=s).to(dev).to(dtype)
+    torch.manual_seed(C + H)
     x = torch.randn(B, C, H, W, device=dev).to(dtype).contiguous(memory_format=torch.channels_last)
     with torch.no_grad():
-        got = pack_frontend(x, conv)
+        got = pack_frontend(x)
     assert got is not None
-    x_nchw, raw, pooled = got
+    x_nchw, pooled = got
     assert x_nchw.is_contiguous() and torch.equal(x_nchw, x)
     xd = x.double().cpu()
-    want_raw = torch.nn.functional.conv2d(xd, conv.weight.detach().double().cpu(),
-                                          conv.bias.detach().double().cpu(), stride=s)
-    assert raw.shape == want_raw.shape and raw.is_contiguous()
-    tol = {"f32": 1e-5, "f16": 2e-3, "bf16": 1e-2}[dt]
-    err = (raw.double().cpu() - want_raw).abs()
-    assert (err <= tol * want_raw.abs() + tol * want_raw.abs().max()).all(), err.max().item()
     nt = (H * W + 63) // 64
     assert pooled.shape == (B, nt, C) and pooled.dtype == torch.float32
     want_sum = xd.sum(dim=(2, 3))
@@ -43,12 +34,12 @@ def test_frontend_matches_torch(case, dt):
     assert (got_sum - want_sum).abs().max().item() <= 1e-4 * max(1.0, want_sum.abs().max().item())
 
 
-def test_pooled_sums_only():
+def test_pooled_sums_of_half_input():
     from ddfnet_b200.modules import pack_frontend
     dev = torch.device("cuda:0")
     x = torch.randn(3, 128, 28, 28, device=dev).half().contiguous(memory_format=torch.channels_last)
-    x_nchw, raw, pooled = pack_frontend(x)
-    assert raw is None and torch.equal(x_nchw, x)
+    x_nchw, pooled = pack_frontend(x)
+    assert torch.equal(x_nchw, x)
     want = x.double().sum(dim=(2, 3))
     assert (pooled.double().sum(dim=1) - want).abs().max().item() <= 1e-3
 
@@ -56,12 +47,11 @@ def test_pooled_sums_only():
 def test_nchw_input_or_gradients_decline():
     from ddfnet_b200.modules import pack_frontend
     dev = torch.device("cuda:0")
-    conv = nn.Conv2d(32, 9, 1).to(dev)
     x = torch.randn(2, 32, 8, 8, device=dev)
     with torch.no_grad():
-        assert pack_frontend(x, conv) is None                      # contiguous NCHW: nothing to convert
-    xcl = x.contiguous(memory_format=torch.channels_last)
-    assert pack_frontend(xcl, conv) is None                        # parameters require grad
+        assert pack_frontend(x) is None                            # contiguous NCHW: nothing to convert
+    xcl = x.contiguous(memory_format=torch.channels_last).requires_grad_()
+    assert pack_frontend(xcl) is None                              # gradients are being recorded
 
 
 @pytest.mark.parametrize("cfg", [
