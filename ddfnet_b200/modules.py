@@ -8,6 +8,8 @@ Plain PyTorch; only the ``ddf`` call reaches the CUDA kernels.
 """
 from __future__ import annotations
 
+import weakref
+
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
@@ -90,6 +92,20 @@ def build_channel_branch(in_channels, kernel_size, nonlinearity='relu', se_ratio
         FilterNorm(in_channels, kernel_size, 'channel', nonlinearity, running_std=True))
 
 
+# Tensors derived from a module's parameters (re-laid-out or padded weights, folded affine
+# maps), keyed by the module and kept outside it: they never reach a state_dict or a pickle
+# and disappear with the module.  Each entry carries the (data_ptr, _version) key of the
+# parameters it was built from and is rebuilt when that changes.
+_DERIVED: "weakref.WeakKeyDictionary[nn.Module, dict]" = weakref.WeakKeyDictionary()
+
+
+def _derived(module: nn.Module) -> dict:
+    d = _DERIVED.get(module)
+    if d is None:
+        d = _DERIVED[module] = {}
+    return d
+
+
 def pack_frontend(x: torch.Tensor):
     """One pass over a channels_last ``x`` through ``ddf_b200_pack_frontend``: (x as contiguous
     NCHW, per-tile channel sums (B, NT, C) float32).  Returns None when the case is outside the
@@ -122,14 +138,14 @@ def _padded_spatial_conv(conv: nn.Conv2d):
     gp = (g + 15) // 16 * 16
     key = (conv.weight.data_ptr(), conv.weight._version, conv.bias.data_ptr(), conv.bias._version,
            conv.weight.dtype)
-    cache = getattr(conv, "_ddf_padded", None)
+    cache = _derived(conv).get("padded")
     if cache is None or cache[0] != key:
         w = torch.zeros((gp, c, 1, 1), dtype=conv.weight.dtype, device=conv.weight.device)
         w[:g] = conv.weight.detach()
         w = w.contiguous(memory_format=torch.channels_last)
         cache = (key, w, torch.ones(g, dtype=torch.float32, device=w.device),
                  conv.bias.detach().float().contiguous())
-        conv._ddf_padded = cache
+        _derived(conv)["padded"] = cache
     return cache[1], cache[2], cache[3]
 
 
@@ -186,11 +202,11 @@ def channel_filter_fused(branch: nn.Sequential, x: torch.Tensor, kernel_size: in
     if c % 8 != 0 or c % cw != 0:
         return None
     key = (conv2.weight.data_ptr(), conv2.weight._version, conv2.weight.dtype)
-    cache = getattr(branch, "_ddf_w2s", None)
+    cache = _derived(branch).get("w2s")
     if cache is None or cache[0] != key:
         w2s = conv2.weight.detach().reshape(c // cw, cw, kernel_size ** 2, mid).permute(0, 3, 2, 1).contiguous()
         cache = (key, w2s)
-        branch._ddf_w2s = cache
+        _derived(branch)["w2s"] = cache
     w2 = cache[1]
     with torch.cuda.device(x.device):
         _lib.check(lib.ddf_b200_channel_filter(

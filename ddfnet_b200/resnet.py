@@ -17,7 +17,7 @@ import torch
 import torch.nn as nn
 
 from .layout import to_channels_last
-from .modules import DDFPack
+from .modules import DDFPack, _derived
 
 
 class DDFBottleneck(nn.Module):
@@ -39,7 +39,6 @@ class DDFBottleneck(nn.Module):
         self.act3 = nn.ReLU(inplace=True)
         self.downsample = downsample
         self.fused_inference = False  # set by fold_batchnorm(..., fuse_activations=True)
-        self._bn2_affine = None
 
     def forward(self, x):
         if self.fused_inference:
@@ -55,12 +54,15 @@ class DDFBottleneck(nn.Module):
     def _bn2_scale_shift(self, device):
         # The eval-mode BatchNorm after the DDFPack as a float32 per-channel affine map; kept
         # outside the module's buffers so that .half() / .to(dtype) leave it in float32.
-        if self._bn2_affine is None or self._bn2_affine[0].device != device:
-            bn = self.bn2
+        bn = self.bn2
+        key = tuple((t.data_ptr(), t._version) for t in (bn.weight, bn.bias, bn.running_mean, bn.running_var))
+        cache = _derived(self).get("bn2_affine")
+        if cache is None or cache[0] != key or cache[1].device != device:
             scale = bn.weight.detach().float() / torch.sqrt(bn.running_var.float() + bn.eps)
             shift = bn.bias.detach().float() - bn.running_mean.float() * scale
-            self._bn2_affine = (scale.contiguous(), shift.contiguous())
-        return self._bn2_affine
+            cache = (key, scale.contiguous().to(device), shift.contiguous().to(device))
+            _derived(self)["bn2_affine"] = cache
+        return cache[1], cache[2]
 
     def _forward_fused(self, x):
         # After fold_batchnorm: conv1 + bias + ReLU and conv3 + bias + shortcut + ReLU each as
@@ -168,7 +170,6 @@ def fold_batchnorm(model: "DDFResNet", fuse_activations: bool = False) -> "DDFRe
     for m in model.modules():
         if isinstance(m, DDFBottleneck):
             m.fused_inference = fuse_activations
-            m._bn2_affine = None  # rebuilt lazily from bn2 on first use
     model.conv1, model.bn1 = _fold(model.conv1, model.bn1), nn.Identity()
     for m in model.modules():
         if isinstance(m, DDFBottleneck):
