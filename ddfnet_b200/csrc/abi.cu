@@ -7,6 +7,7 @@
 #include "common.cuh"
 #include "generic.cuh"
 #include "ring_fwd.cuh"
+#include "row_fwd.cuh"
 #include "stream_fwd.cuh"
 
 #include <cstdlib>
@@ -241,6 +242,18 @@ static int run_ring(const RingArgs& a, cudaStream_t st) {
     return rc;
 }
 
+// Row kernel (7 x 7 outputs, 2-byte element types).
+static int run_row(const RowArgs& a, cudaStream_t st) {
+    int rc;
+    switch (a.p.dtype) {
+        case DDF_B200_F16: rc = row_dispatch<__half>(a, st); break;
+        case DDF_B200_BF16: rc = row_dispatch<__nv_bfloat16>(a, st); break;
+        default: rc = kNotHandled;
+    }
+    if (rc == 0) g_launches.fetch_add(1, std::memory_order_relaxed);
+    return rc;
+}
+
 // AUTO prefers the streaming kernels once there is at least one plane group per SM
 // and a quarter megabyte of input; below that the generic kernels launch faster.
 static bool stream_worthwhile(const Problem& p, int sm_count) {
@@ -264,6 +277,9 @@ static int forward_impl(const Problem& p, const void* x, const void* cf, const v
             RingArgs ra{x, cf, sf, out, p, false, di->sm_count, di->fault, di->index,
                         true, 0, 0u};
             rc = run_ring(ra, st);
+            if (rc != kNotHandled) return rc;
+            RowArgs wa{x, cf, sf, out, p, di->sm_count, di->fault, di->index};
+            rc = run_row(wa, st);
             if (rc != kNotHandled) return rc;
         }
         if (P > 0 && want) {

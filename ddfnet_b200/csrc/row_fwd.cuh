@@ -1,0 +1,408 @@
+// Row kernel: DDF forward for planes whose output is 7 x 7 (the last ddf_resnet stage: 7 x 7 at
+// stride 1 and 14 x 14 -> 7 x 7 at stride 2), k = 3, dilation 1, 2-byte element types.
+//
+// Such planes are tiny (98 or 392 bytes in, 98 bytes out) and there are tens of thousands of
+// them; what a launch costs is the time until the first arithmetic starts and the number of
+// instructions per output, not HBM time.  Hence:
+//
+//  * A thread owns one whole output row (7 pixels) of one plane per chunk of 64 planes, and
+//    the same row position for the whole kernel: the 9 x 7 spatial-filter values of its row
+//    stay in registers (36 words) across all planes of a sample.  Because the row spans the
+//    full width, the left and right zero padding is known at compile time: those taps are
+//    simply not emitted (57 instead of 63 taps), and no halo masks exist.  Rows above and
+//    below the plane are redirected by one address select to a zeroed area.
+//  * Rows of 7 two-byte elements start on odd element offsets in every other row.  A row is
+//    read as four aligned words and brought into a fixed register layout by funnel shifts
+//    whose shift amount (0 or 16) is a per-thread constant; the arithmetic then selects
+//    fixed halves of fixed registers (mixed-precision FMA, see ring_fwd.cuh).  At stride 2
+//    the input rows (14 elements) are word aligned and need no shifts.
+//  * The 7 results of a row go to global memory as three word stores and one 2-byte store;
+//    a warp's stores cover 448 contiguous bytes.
+//  * Persistent CTA per SM; chunks of 64 planes (plus their channel filters) arrive through a
+//    ring of shared-memory slots filled by untiled TMA bulk copies from one producer lane; a
+//    conversion warp turns each landed chunk's channel filters into the per-plane vector
+//    layout; 14 compute warps.  All of a CTA's chunks are usually in flight at once (a CTA's
+//    share is about 7 chunks), so the loads are limited by HBM, not by round trips.
+//
+// Every mbarrier wait is bounded by the plan's wait_cycles (fault word + return, as in the
+// other streaming kernels).
+#pragma once
+
+#include <atomic>
+
+#include "common.cuh"
+#include "ring_fwd.cuh"
+
+namespace ddf {
+
+struct RowPlan {
+    const void* in;
+    const void* cf;
+    const void* sf;
+    void* out;
+    int chunks_per_sample;    // C / 64
+    int n_slots;
+    long long total_chunks;   // B * C / 64
+    uint32_t chunk_bytes;     // 64 planes of input
+    uint32_t sf_bytes;        // 9 * 49 * 2
+    unsigned long long sf_total;
+    uint32_t off_zero, off_sf, sf_stride, off_stage0, stage_stride, off_rawcf, off_conv;
+    int* fault;
+    long long wait_cycles;
+};
+
+constexpr int kRowChunk = 64;                 // planes per chunk
+constexpr int kRowCompute = kRowChunk * 7;    // compute threads: one per (plane, output row)
+constexpr int kRowThreads = kRowCompute + 64; // + producer warp + conversion warp
+constexpr int kRowMaxSlots = 16;
+constexpr int kRowCFP = 48;                   // bytes per plane of the converted channel filter
+
+__device__ __forceinline__ void stg32(void* p, uint32_t v) {
+    asm volatile("st.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void stg16(void* p, uint32_t v) {
+    asm volatile("st.global.b16 [%0], %1;" ::"l"(p), "h"((uint16_t)v) : "memory");
+}
+
+template <typename T, int S, int MODE>
+__global__ void __launch_bounds__(kRowThreads, 1)
+row_kernel(const __grid_constant__ RowPlan pl) {
+    constexpr int K = 3, KK = 9, OW = 7;
+    constexpr int W = OW * S;                       // input row length in elements
+    constexpr int PLANE = W * W * 2;                // input plane bytes
+    constexpr int NW = S == 1 ? 4 : 7;              // words of an input row a thread holds
+    static_assert(S == 1 || S == 2, "stride 1 or 2");
+    static_assert(sizeof(T) == 2, "2-byte element types only");
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const uint32_t sbase = smem_u32(smem_raw);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int NST = pl.n_slots;
+    constexpr int NCW = kRowCompute / 32;           // 14 compute warps
+
+#define WBAR_FULL(s) (sbase + 8u * (uint32_t)(s))
+#define WBAR_EMPTY(s) (sbase + 8u * (uint32_t)(kRowMaxSlots + (s)))
+#define WBAR_CF(s) (sbase + 8u * (uint32_t)(2 * kRowMaxSlots + (s)))
+#define WBAR_SF_FULL(i) (sbase + 8u * (uint32_t)(3 * kRowMaxSlots + (i)))
+#define WBAR_SF_EMPTY(i) (sbase + 8u * (uint32_t)(3 * kRowMaxSlots + 2 + (i)))
+#define WSTAGE(s) (sbase + pl.off_stage0 + (uint32_t)(s) * pl.stage_stride)
+
+    if (tid == 0) {
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(WBAR_FULL(s), 1);
+            mbar_init(WBAR_EMPTY(s), (uint32_t)NCW);
+            mbar_init(WBAR_CF(s), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(WBAR_SF_FULL(i), 1);
+            mbar_init(WBAR_SF_EMPTY(i), (uint32_t)NCW);
+        }
+        mbar_fence_init();
+    }
+    if (tid < 4) sts128(sbase + pl.off_zero + 16u * (uint32_t)tid, 0u, 0u, 0u, 0u);
+    __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    const long long chunk_lo = (pl.total_chunks * (long long)blockIdx.x) / gridDim.x;
+    const long long chunk_hi = (pl.total_chunks * (long long)(blockIdx.x + 1)) / gridDim.x;
+    const int my_chunks = (int)(chunk_hi - chunk_lo);
+    if (my_chunks == 0) return;
+    const int CPS = pl.chunks_per_sample;
+
+    if (warp == NCW) {
+        // ------------------------------------------------------------- producer lane
+        if (lane != 0) return;
+        bool ok = true;
+        int seg = 0, issued = 0;
+        int b = (int)(chunk_lo / CPS);
+        int left_in_sample = 0;                    // chunks of sample b still to issue (0: start a sample)
+        int first_left = CPS - (int)(chunk_lo - (long long)b * CPS);
+        int slot = 0, round = 0;                   // chunk i uses slot i % NST in round i / NST
+        for (int i = 0; i < my_chunks && ok; ++i) {
+            const long long g = chunk_lo + i;
+            if (left_in_sample == 0) {
+                // this sample's spatial filter, into the buffer the sample before the previous one used
+                const int buf = seg & 1;
+                if (seg >= 2) ok = mbar_wait_for(WBAR_SF_EMPTY(buf), (uint32_t)(((seg >> 1) - 1) & 1), pl.wait_cycles);
+                if (!ok) break;
+                const unsigned long long g0 = (unsigned long long)b * pl.sf_bytes;
+                const Span sp = span_prepare(sbase + pl.off_sf + (uint32_t)buf * pl.sf_stride, pl.sf, g0,
+                                             g0 + pl.sf_bytes, pl.sf_total);
+                mbar_arrive_expect_tx(WBAR_SF_FULL(buf), sp.bytes);
+                span_issue(sp, WBAR_SF_FULL(buf));
+                ++seg;
+                left_in_sample = i == 0 ? first_left : CPS;
+            }
+            if (--left_in_sample == 0) ++b;
+            if (round > 0) ok = mbar_wait_for(WBAR_EMPTY(slot), (uint32_t)((round - 1) & 1), pl.wait_cycles);
+            if (!ok) break;
+            const uint32_t cfb = (uint32_t)(kRowChunk * KK * 2);
+            mbar_arrive_expect_tx(WBAR_FULL(slot), pl.chunk_bytes + cfb);
+            bulk_g2s(WSTAGE(slot), (const char*)pl.in + (unsigned long long)g * pl.chunk_bytes, pl.chunk_bytes,
+                     WBAR_FULL(slot));
+            bulk_g2s(WSTAGE(slot) + pl.off_rawcf, (const char*)pl.cf + (unsigned long long)g * cfb, cfb,
+                     WBAR_FULL(slot));
+            issued = i + 1;
+            if (++slot == NST) { slot = 0; ++round; }
+        }
+        if (!ok) atomicCAS(pl.fault, 0, (int)kFaultService);
+        // do not leave while requested copies may still be in flight (bounded)
+        bool landed = true;
+        for (int j = (issued > NST ? issued - NST : 0); j < issued; ++j)
+            landed &= mbar_wait_for(WBAR_FULL(j % NST), (uint32_t)((j / NST) & 1), pl.wait_cycles);
+        for (int s2 = (seg > 2 ? seg - 2 : 0); s2 < seg; ++s2)
+            landed &= mbar_wait_for(WBAR_SF_FULL(s2 & 1), (uint32_t)((s2 >> 1) & 1), pl.wait_cycles);
+        if (!landed) atomicCAS(pl.fault, 0, (int)kFaultDrain);
+        return;
+    }
+    if (warp == NCW + 1) {
+        // ------------------------------------------------- channel-filter conversion warp
+        // raw 2-byte filters of a landed chunk -> per plane: KK floats (mul) or KK aligned
+        // 2-byte values (add) every kRowCFP bytes
+        int slot = 0;
+        uint32_t ph = 0u;
+        for (int i = 0; i < my_chunks; ++i) {
+            if (!mbar_wait_for(WBAR_FULL(slot), ph, pl.wait_cycles)) {
+                atomicCAS(pl.fault, 0, (int)kFaultConsumerFull);
+                return;
+            }
+            const uint32_t src = WSTAGE(slot) + pl.off_rawcf;
+            const uint32_t dst = WSTAGE(slot) + pl.off_conv;
+#pragma unroll 3
+            for (int e = lane; e < kRowChunk * KK; e += 32) {
+                const int u = e / KK, t = e - u * KK;
+                const uint32_t raw = lds16(src + 2u * (uint32_t)e);
+                if constexpr (MODE == DDF_B200_MUL) sts32(dst + (uint32_t)(u * kRowCFP + 4 * t), Mix<T>::f32_bits(raw));
+                else sts16(dst + (uint32_t)(u * kRowCFP + 2 * t), raw);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(WBAR_CF(slot));
+            if (++slot == NST) { slot = 0; ph ^= 1u; }
+        }
+        return;
+    }
+
+    // ------------------------------------------------------------------- compute warps
+    const int j = tid / 7, y = tid - 7 * j;   // plane within the chunk, output row
+    // Input rows of this thread relative to its plane: byte offset of the aligned word the
+    // row is read from, funnel shift that brings element 0 to the low half of word 0, and
+    // whether the row lies outside the plane.
+    uint32_t rowoff[K], rowsh[K];
+    bool rowout[K];
+#pragma unroll
+    for (int r = 0; r < K; ++r) {
+        const int iy = y * S - 1 + r;
+        rowout[r] = iy < 0 || iy >= W;
+        const uint32_t a = (uint32_t)(j * PLANE + iy * W * 2);   // (wraps for iy < 0: unused then)
+        rowoff[r] = S == 1 ? (a & ~3u) : a;
+        rowsh[r] = S == 1 ? (a & 2u) * 8u : 0u;
+    }
+    const uint32_t zaddr = sbase + pl.off_zero + (S == 2 ? 4u : 0u);
+    const uint32_t cfoff = pl.off_conv + (uint32_t)(j * kRowCFP);
+    // output: 7 elements at element offset plane * 49 + 7 y; its word parity is a thread constant
+    // (a chunk starts on an even plane)
+    const uint32_t opar = (uint32_t)((j + y) & 1);
+    const uint32_t osh = opar * 16u;
+    char* outp = reinterpret_cast<char*>(pl.out) +
+                 ((unsigned long long)chunk_lo * kRowChunk + (unsigned long long)j) * (OW * OW * 2) +
+                 (unsigned long long)(y * OW * 2);
+
+    uint32_t sfw[KK][4];
+#pragma unroll
+    for (int t = 0; t < KK; ++t)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) sfw[t][q] = 0u;
+
+    int seg = 0, slot = 0;
+    uint32_t ph = 0u;
+    int b = (int)(chunk_lo / CPS);
+    int left_in_sample = 0;   // chunks of the current sample still to come (0: the next chunk starts a sample)
+    const int first_left = CPS - (int)(chunk_lo - (long long)b * CPS);
+#pragma unroll 1
+    for (int i = 0; i < my_chunks; ++i) {
+        if (!mbar_wait_for(WBAR_CF(slot), ph, pl.wait_cycles) ||
+            !mbar_wait_for(WBAR_FULL(slot), ph, pl.wait_cycles)) {
+            atomicCAS(pl.fault, 0, (int)kFaultConsumerFull);
+            return;
+        }
+        if (left_in_sample == 0) {
+            // a new sample: its spatial filter row (9 taps x 7 pixels) into registers, as
+            // (p0,p1) (p2,p3) (p4,p5) (p6,-) per tap
+            const int buf = seg & 1;
+            if (!mbar_wait_for(WBAR_SF_FULL(buf), (uint32_t)((seg >> 1) & 1), pl.wait_cycles)) {
+                atomicCAS(pl.fault, 0, (int)kFaultConsumerSf);
+                return;
+            }
+            const uint32_t sfs = sbase + pl.off_sf + (uint32_t)buf * pl.sf_stride +
+                                 (uint32_t)(((unsigned long long)b * pl.sf_bytes) & 15ull) + (uint32_t)(y * OW * 2);
+#pragma unroll
+            for (int t = 0; t < KK; ++t) {
+                const uint32_t a = sfs + (uint32_t)(t * OW * OW * 2);
+                const uint32_t aw = a & ~3u, sh = (a & 2u) * 8u;
+                const uint32_t w0 = lds32(aw), w1 = lds32(aw + 4), w2 = lds32(aw + 8), w3 = lds32(aw + 12);
+                sfw[t][0] = __funnelshift_r(w0, w1, sh);
+                sfw[t][1] = __funnelshift_r(w1, w2, sh);
+                sfw[t][2] = __funnelshift_r(w2, w3, sh);
+                sfw[t][3] = w3 >> sh;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(WBAR_SF_EMPTY(buf));
+            ++seg;
+            left_in_sample = i == 0 ? first_left : CPS;
+        }
+        if (--left_in_sample == 0) ++b;
+
+        const uint32_t st = WSTAGE(slot);
+        // ---- the plane's input rows
+        uint32_t xw[K][NW];
+#pragma unroll
+        for (int r = 0; r < K; ++r) {
+            const uint32_t a = rowout[r] ? zaddr : st + rowoff[r];
+            if constexpr (S == 1) {
+                const uint32_t w0 = lds32(a), w1 = lds32(a + 4), w2 = lds32(a + 8), w3 = lds32(a + 12);
+                xw[r][0] = __funnelshift_r(w0, w1, rowsh[r]);
+                xw[r][1] = __funnelshift_r(w1, w2, rowsh[r]);
+                xw[r][2] = __funnelshift_r(w2, w3, rowsh[r]);
+                xw[r][3] = w3 >> rowsh[r];
+            } else {
+                // 14 elements = 7 words; the middle row is 8-byte aligned, the outer two are not
+                if (r == 1) {
+                    lds64(a, xw[r][0], xw[r][1]);
+                    lds64(a + 8, xw[r][2], xw[r][3]);
+                    lds64(a + 16, xw[r][4], xw[r][5]);
+                    xw[r][6] = lds32(a + 24);
+                } else {
+                    xw[r][0] = lds32(a);
+                    lds64(a + 4, xw[r][1], xw[r][2]);
+                    lds64(a + 12, xw[r][3], xw[r][4]);
+                    lds64(a + 20, xw[r][5], xw[r][6]);
+                }
+            }
+        }
+        // ---- the plane's channel filter
+        uint32_t c[12];
+        {
+            const uint32_t ca = st + cfoff;
+            if constexpr (MODE == DDF_B200_MUL) {
+                lds128(ca, c[0], c[1], c[2], c[3]);
+                lds128(ca + 16, c[4], c[5], c[6], c[7]);
+                c[8] = lds32(ca + 32);
+            } else {
+                lds128(ca, c[0], c[1], c[2], c[3]);
+                c[4] = lds32(ca + 16);
+            }
+        }
+        // ---- 57 taps (the 6 that fall left or right of the plane are not emitted), tap-major
+        float acc[OW];
+#pragma unroll
+        for (int p = 0; p < OW; ++p) acc[p] = 0.f;
+#pragma unroll
+        for (int t = 0; t < KK; ++t) {
+            const int ti = t / K, tj = t % K;
+#pragma unroll
+            for (int p = 0; p < OW; ++p) {
+                const int e = p * S + tj - 1;   // element of the input row
+                if (e < 0 || e >= W) continue;
+                if constexpr (MODE == DDF_B200_MUL) {
+                    const float yv = Mix<T>::fmaw(e & 1, p & 1, xw[ti][e >> 1], sfw[t][p >> 1], 0.f);
+                    acc[p] = fmaf(yv, __uint_as_float(c[t]), acc[p]);
+                } else {
+                    acc[p] = Mix<T>::fmaw(e & 1, p & 1, xw[ti][e >> 1], sfw[t][p >> 1], acc[p]);
+                    acc[p] = Mix<T>::fmaw(e & 1, t & 1, xw[ti][e >> 1], c[t >> 1], acc[p]);
+                }
+            }
+        }
+        // ---- store 7 results: three words and one half, arranged by the row's word parity
+        {
+            const uint32_t w0 = Word<T>::put(acc[0], acc[1]), w1 = Word<T>::put(acc[2], acc[3]);
+            const uint32_t w2 = Word<T>::put(acc[4], acc[5]), w3 = Word<T>::put(acc[6], 0.f);
+            const uint32_t v0 = __funnelshift_r(w0, w1, osh), v1 = __funnelshift_r(w1, w2, osh);
+            const uint32_t v2 = __funnelshift_r(w2, w3, osh);
+            char* pw = outp + 2u * opar;
+            stg32(pw, v0);
+            stg32(pw + 4, v1);
+            stg32(pw + 8, v2);
+            stg16(outp + (opar ? 0 : 12), opar ? w0 : w3);
+        }
+        outp += kRowChunk * OW * OW * 2;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(WBAR_EMPTY(slot));
+        if (++slot == NST) { slot = 0; ph ^= 1u; }
+    }
+#undef WBAR_FULL
+#undef WBAR_EMPTY
+#undef WBAR_CF
+#undef WBAR_SF_FULL
+#undef WBAR_SF_EMPTY
+#undef WSTAGE
+}
+
+// ------------------------------------------------------------------------ host side
+struct RowArgs {
+    const void* in;
+    const void* cf;
+    const void* sf;
+    void* out;
+    Problem p;
+    int sm_count;
+    int* fault;
+    int device;
+};
+
+template <typename T, int S, int MODE>
+int row_launch(const RowArgs& a, cudaStream_t stream) {
+    const Problem& p = a.p;
+    constexpr int W = 7 * S;
+    RowPlan pl;
+    pl.in = a.in; pl.cf = a.cf; pl.sf = a.sf; pl.out = a.out;
+    pl.chunks_per_sample = p.C / kRowChunk;
+    pl.total_chunks = (long long)p.B * pl.chunks_per_sample;
+    pl.chunk_bytes = (uint32_t)(kRowChunk * W * W * 2);
+    pl.sf_bytes = 9u * 49u * 2u;
+    pl.sf_total = (unsigned long long)p.B * pl.sf_bytes;
+    pl.off_zero = round_up(8u * (3 * kRowMaxSlots + 4), 16);
+    pl.off_sf = round_up(pl.off_zero + 64u, 128);
+    pl.sf_stride = round_up(pl.sf_bytes + 48u, 128);
+    pl.off_stage0 = pl.off_sf + 2u * pl.sf_stride;
+    pl.off_rawcf = round_up(pl.chunk_bytes + 16u, 16);      // a row's last word load may run 14 bytes over
+    pl.off_conv = round_up(pl.off_rawcf + (uint32_t)(kRowChunk * 9 * 2), 16);
+    pl.stage_stride = round_up(pl.off_conv + (uint32_t)(kRowChunk * kRowCFP), 128);
+    const long long share = (pl.total_chunks + a.sm_count - 1) / a.sm_count;
+    int slots = (int)((kSmemBudget - pl.off_stage0) / pl.stage_stride);
+    if (slots > kRowMaxSlots) slots = kRowMaxSlots;
+    if (slots > share) slots = (int)share;
+    if (slots < 2) slots = share < 2 ? 1 : 2;
+    if (pl.off_stage0 + (uint32_t)slots * pl.stage_stride > kSmemBudget) return kNotHandled;
+    pl.n_slots = slots;
+    pl.fault = a.fault;
+    pl.wait_cycles = kWaitCycles;
+    const uint32_t smem = pl.off_stage0 + (uint32_t)slots * pl.stage_stride;
+    const int grid = (int)(pl.total_chunks < a.sm_count ? pl.total_chunks : a.sm_count);
+    auto kern = row_kernel<T, S, MODE>;
+    static std::atomic<unsigned long long> opted_in{0};
+    const unsigned long long bit = 1ull << (a.device & 63);
+    if (!(opted_in.load(std::memory_order_acquire) & bit)) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
+        if (e != cudaSuccess) return (int)e;
+        opted_in.fetch_or(bit, std::memory_order_release);
+    }
+    return (int)launch_overlapped(kern, dim3((unsigned)grid), dim3((unsigned)kRowThreads), smem, stream, true, pl);
+}
+
+// The problems the row kernel is built for.
+inline bool row_applicable(const RowArgs& a) {
+    const Problem& p = a.p;
+    if (p.dtype != DDF_B200_F16 && p.dtype != DDF_B200_BF16) return false;
+    if (p.k != 3 || p.d != 1 || (p.s != 1 && p.s != 2) || p.sf_norm) return false;
+    if (p.OH != 7 || p.OW != 7 || p.H != 7 * p.s || p.W != 7 * p.s) return false;
+    if (p.C % kRowChunk != 0) return false;
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    return al16(a.in) && al16(a.cf) && al16(a.sf) && al16(a.out);
+}
+
+// Defined per element type in row_inst_<type>.cu.
+template <typename T>
+int row_dispatch(const RowArgs& a, cudaStream_t stream);
+
+}  // namespace ddf

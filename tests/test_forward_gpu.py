@@ -73,6 +73,11 @@ STREAM = [
     (3, 48, 14, 14, 3, 1, 1),    # plane-ring: sixteen planes per pass
     (5, 40, 28, 28, 3, 1, 2),    # plane-ring, stride 2
     (2, 8, 57, 56, 3, 1, 1),     # 56 wide but 57 high: ring kernel with a non-square plane
+    (3, 128, 7, 7, 3, 1, 1),     # row kernel (2-byte types): two chunks per sample
+    (400, 64, 7, 7, 3, 1, 1),    # row kernel: a new sample every chunk, both filter buffers reused
+    (2400, 64, 7, 7, 3, 1, 1),   # row kernel: more chunks per CTA than ring slots
+    (3, 192, 14, 14, 3, 1, 2),   # row kernel, stride 2
+    (1100, 64, 14, 14, 3, 1, 2), # row kernel, stride 2: ring slots reused
 ]
 
 
