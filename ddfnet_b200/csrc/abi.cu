@@ -276,10 +276,10 @@ static int forward_impl(const Problem& p, const void* x, const void* cf, const v
         if (want) {
             RingArgs ra{x, cf, sf, out, p, false, di->sm_count, di->fault, di->index,
                         true, 0, 0u};
-            rc = run_ring(ra, st);
-            if (rc != kNotHandled) return rc;
             RowArgs wa{x, cf, sf, out, p, di->sm_count, di->fault, di->index};
             rc = run_row(wa, st);
+            if (rc != kNotHandled) return rc;
+            rc = run_ring(ra, st);
             if (rc != kNotHandled) return rc;
         }
         if (P > 0 && want) {

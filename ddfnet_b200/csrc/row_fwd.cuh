@@ -1,24 +1,25 @@
-// Row kernel: DDF forward for planes whose output is 7 x 7 (the last ddf_resnet stage: 7 x 7 at
-// stride 1 and 14 x 14 -> 7 x 7 at stride 2), k = 3, dilation 1, 2-byte element types.
+// Row kernel: DDF forward for planes whose output is 7 x 7 or 14 x 14 (the last two ddf_resnet
+// stages: 7 x 7 and 14 x 14 at stride 1, 14 x 14 -> 7 x 7 at stride 2), k = 3, dilation 1, 2-byte
+// element types.
 //
-// Such planes are tiny (98 or 392 bytes in, 98 bytes out) and there are tens of thousands of
-// them; what a launch costs is the time until the first arithmetic starts and the number of
-// instructions per output, not HBM time.  Hence:
+// Such planes are tiny (98 to 392 bytes) and there are tens of thousands of them; what a
+// launch costs is the time until the first arithmetic starts and the number of instructions
+// per output, not HBM time.  Hence:
 //
-//  * A thread owns one whole output row (7 pixels) of one plane per chunk of 64 planes, and
-//    the same row position for the whole kernel: the 9 x 7 spatial-filter values of its row
-//    stay in registers (36 words) across all planes of a sample.  Because the row spans the
+//  * A thread owns one whole output row (OW = 7 or 14 pixels) of one plane per chunk of 448 / OW
+//    planes, and the same row position for the whole kernel: the 9 x OW spatial-filter values
+//    of its row stay in registers across all planes of a sample.  Because the row spans the
 //    full width, the left and right zero padding is known at compile time: those taps are
-//    simply not emitted (57 instead of 63 taps), and no halo masks exist.  Rows above and
-//    below the plane are redirected by one address select to a zeroed area.
+//    simply not emitted (57 instead of 63 taps at OW = 7), and no halo masks exist.  Rows above
+//    and below the plane are redirected by one address select to a zeroed area.
 //  * Rows of 7 two-byte elements start on odd element offsets in every other row.  A row is
 //    read as four aligned words and brought into a fixed register layout by funnel shifts
 //    whose shift amount (0 or 16) is a per-thread constant; the arithmetic then selects
-//    fixed halves of fixed registers (mixed-precision FMA, see ring_fwd.cuh).  At stride 2
-//    the input rows (14 elements) are word aligned and need no shifts.
-//  * The 7 results of a row go to global memory as three word stores and one 2-byte store;
-//    a warp's stores cover 448 contiguous bytes.
-//  * Persistent CTA per SM; chunks of 64 planes (plus their channel filters) arrive through a
+//    fixed halves of fixed registers (mixed-precision FMA, see ring_fwd.cuh).  Rows of 14
+//    elements are word aligned and need no shifts.
+//  * The results of a row go to global memory as word stores (three words and one 2-byte
+//    store for 7 pixels); a warp's stores cover a contiguous run.
+//  * Persistent CTA per SM; chunks of planes (plus their channel filters) arrive through a
 //    ring of shared-memory slots filled by untiled TMA bulk copies from one producer lane; a
 //    conversion warp turns each landed chunk's channel filters into the per-plane vector
 //    layout; 14 compute warps.  All of a CTA's chunks are usually in flight at once (a CTA's
@@ -40,19 +41,18 @@ struct RowPlan {
     const void* cf;
     const void* sf;
     void* out;
-    int chunks_per_sample;    // C / 64
+    int chunks_per_sample;    // C / planes per chunk
     int n_slots;
-    long long total_chunks;   // B * C / 64
-    uint32_t chunk_bytes;     // 64 planes of input
-    uint32_t sf_bytes;        // 9 * 49 * 2
+    long long total_chunks;   // B * C / planes per chunk
+    uint32_t chunk_bytes;     // one chunk of input planes
+    uint32_t sf_bytes;        // 9 * OW * OW * 2
     unsigned long long sf_total;
     uint32_t off_zero, off_sf, sf_stride, off_stage0, stage_stride, off_rawcf, off_conv;
     int* fault;
     long long wait_cycles;
 };
 
-constexpr int kRowChunk = 64;                 // planes per chunk
-constexpr int kRowCompute = kRowChunk * 7;    // compute threads: one per (plane, output row)
+constexpr int kRowCompute = 448;              // compute threads: one per (plane, output row) of a chunk
 constexpr int kRowThreads = kRowCompute + 64; // + producer warp + conversion warp
 constexpr int kRowMaxSlots = 16;
 constexpr int kRowCFP = 48;                   // bytes per plane of the converted channel filter
@@ -64,14 +64,19 @@ __device__ __forceinline__ void stg16(void* p, uint32_t v) {
     asm volatile("st.global.b16 [%0], %1;" ::"l"(p), "h"((uint16_t)v) : "memory");
 }
 
-template <typename T, int S, int MODE>
+template <typename T, int S, int OW, int MODE>
 __global__ void __launch_bounds__(kRowThreads, 1)
 row_kernel(const __grid_constant__ RowPlan pl) {
-    constexpr int K = 3, KK = 9, OW = 7;
+    constexpr int K = 3, KK = 9;
+    constexpr int CH = kRowCompute / OW;            // planes per chunk
     constexpr int W = OW * S;                       // input row length in elements
     constexpr int PLANE = W * W * 2;                // input plane bytes
-    constexpr int NW = S == 1 ? 4 : 7;              // words of an input row a thread holds
+    constexpr bool XSHIFT = W % 2 != 0;             // input rows start on odd elements: funnel shifts
+    constexpr bool OSHIFT = OW % 2 != 0;            // the same for output and spatial-filter rows
+    constexpr int NW = (W + 1) / 2;                 // words of an input row a thread holds
+    constexpr int NSW = (OW + 1) / 2;               // words of a spatial-filter / output row
     static_assert(S == 1 || S == 2, "stride 1 or 2");
+    static_assert(W == 7 || W == 14, "input rows of 7 or 14 elements");
     static_assert(sizeof(T) == 2, "2-byte element types only");
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -137,7 +142,7 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             if (--left_in_sample == 0) ++b;
             if (round > 0) ok = mbar_wait_for(WBAR_EMPTY(slot), (uint32_t)((round - 1) & 1), pl.wait_cycles);
             if (!ok) break;
-            const uint32_t cfb = (uint32_t)(kRowChunk * KK * 2);
+            const uint32_t cfb = (uint32_t)(CH * KK * 2);
             mbar_arrive_expect_tx(WBAR_FULL(slot), pl.chunk_bytes + cfb);
             bulk_g2s(WSTAGE(slot), (const char*)pl.in + (unsigned long long)g * pl.chunk_bytes, pl.chunk_bytes,
                      WBAR_FULL(slot));
@@ -170,7 +175,7 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             const uint32_t src = WSTAGE(slot) + pl.off_rawcf;
             const uint32_t dst = WSTAGE(slot) + pl.off_conv;
 #pragma unroll 3
-            for (int e = lane; e < kRowChunk * KK; e += 32) {
+            for (int e = lane; e < CH * KK; e += 32) {
                 const int u = e / KK, t = e - u * KK;
                 const uint32_t raw = lds16(src + 2u * (uint32_t)e);
                 if constexpr (MODE == DDF_B200_MUL) sts32(dst + (uint32_t)(u * kRowCFP + 4 * t), Mix<T>::f32_bits(raw));
@@ -184,7 +189,7 @@ row_kernel(const __grid_constant__ RowPlan pl) {
     }
 
     // ------------------------------------------------------------------- compute warps
-    const int j = tid / 7, y = tid - 7 * j;   // plane within the chunk, output row
+    const int j = tid / OW, y = tid - OW * j;   // plane within the chunk, output row
     // Input rows of this thread relative to its plane: byte offset of the aligned word the
     // row is read from, funnel shift that brings element 0 to the low half of word 0, and
     // whether the row lies outside the plane.
@@ -195,24 +200,24 @@ row_kernel(const __grid_constant__ RowPlan pl) {
         const int iy = y * S - 1 + r;
         rowout[r] = iy < 0 || iy >= W;
         const uint32_t a = (uint32_t)(j * PLANE + iy * W * 2);   // (wraps for iy < 0: unused then)
-        rowoff[r] = S == 1 ? (a & ~3u) : a;
-        rowsh[r] = S == 1 ? (a & 2u) * 8u : 0u;
+        rowoff[r] = XSHIFT ? (a & ~3u) : a;
+        rowsh[r] = XSHIFT ? (a & 2u) * 8u : 0u;
     }
-    const uint32_t zaddr = sbase + pl.off_zero + (S == 2 ? 4u : 0u);
+    const uint32_t zaddr = sbase + pl.off_zero + (S == 2 ? 4u : 0u);   // same alignment class as the rows it replaces
     const uint32_t cfoff = pl.off_conv + (uint32_t)(j * kRowCFP);
-    // output: 7 elements at element offset plane * 49 + 7 y; its word parity is a thread constant
-    // (a chunk starts on an even plane)
-    const uint32_t opar = (uint32_t)((j + y) & 1);
+    // output row: OW elements at element offset plane * OW * OW + OW * y; for odd OW its word
+    // parity is a thread constant (a chunk starts on an even plane)
+    const uint32_t opar = OSHIFT ? (uint32_t)((j + y) & 1) : 0u;
     const uint32_t osh = opar * 16u;
     char* outp = reinterpret_cast<char*>(pl.out) +
-                 ((unsigned long long)chunk_lo * kRowChunk + (unsigned long long)j) * (OW * OW * 2) +
+                 ((unsigned long long)chunk_lo * CH + (unsigned long long)j) * (OW * OW * 2) +
                  (unsigned long long)(y * OW * 2);
 
-    uint32_t sfw[KK][4];
+    uint32_t sfw[KK][NSW];
 #pragma unroll
     for (int t = 0; t < KK; ++t)
 #pragma unroll
-        for (int q = 0; q < 4; ++q) sfw[t][q] = 0u;
+        for (int q = 0; q < NSW; ++q) sfw[t][q] = 0u;
 
     int seg = 0, slot = 0;
     uint32_t ph = 0u;
@@ -227,8 +232,8 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             return;
         }
         if (left_in_sample == 0) {
-            // a new sample: its spatial filter row (9 taps x 7 pixels) into registers, as
-            // (p0,p1) (p2,p3) (p4,p5) (p6,-) per tap
+            // a new sample: its spatial filter row (9 taps x OW pixels) into registers, as
+            // (p0,p1) (p2,p3) ... per tap
             const int buf = seg & 1;
             if (!mbar_wait_for(WBAR_SF_FULL(buf), (uint32_t)((seg >> 1) & 1), pl.wait_cycles)) {
                 atomicCAS(pl.fault, 0, (int)kFaultConsumerSf);
@@ -239,12 +244,17 @@ row_kernel(const __grid_constant__ RowPlan pl) {
 #pragma unroll
             for (int t = 0; t < KK; ++t) {
                 const uint32_t a = sfs + (uint32_t)(t * OW * OW * 2);
-                const uint32_t aw = a & ~3u, sh = (a & 2u) * 8u;
-                const uint32_t w0 = lds32(aw), w1 = lds32(aw + 4), w2 = lds32(aw + 8), w3 = lds32(aw + 12);
-                sfw[t][0] = __funnelshift_r(w0, w1, sh);
-                sfw[t][1] = __funnelshift_r(w1, w2, sh);
-                sfw[t][2] = __funnelshift_r(w2, w3, sh);
-                sfw[t][3] = w3 >> sh;
+                if constexpr (OSHIFT) {
+                    const uint32_t aw = a & ~3u, sh = (a & 2u) * 8u;
+                    const uint32_t w0 = lds32(aw), w1 = lds32(aw + 4), w2 = lds32(aw + 8), w3 = lds32(aw + 12);
+                    sfw[t][0] = __funnelshift_r(w0, w1, sh);
+                    sfw[t][1] = __funnelshift_r(w1, w2, sh);
+                    sfw[t][2] = __funnelshift_r(w2, w3, sh);
+                    sfw[t][3] = w3 >> sh;
+                } else {
+#pragma unroll
+                    for (int q = 0; q < NSW; ++q) sfw[t][q] = lds32(a + 4u * q);
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(WBAR_SF_EMPTY(buf));
@@ -259,14 +269,15 @@ row_kernel(const __grid_constant__ RowPlan pl) {
 #pragma unroll
         for (int r = 0; r < K; ++r) {
             const uint32_t a = rowout[r] ? zaddr : st + rowoff[r];
-            if constexpr (S == 1) {
+            if constexpr (XSHIFT) {
                 const uint32_t w0 = lds32(a), w1 = lds32(a + 4), w2 = lds32(a + 8), w3 = lds32(a + 12);
                 xw[r][0] = __funnelshift_r(w0, w1, rowsh[r]);
                 xw[r][1] = __funnelshift_r(w1, w2, rowsh[r]);
                 xw[r][2] = __funnelshift_r(w2, w3, rowsh[r]);
                 xw[r][3] = w3 >> rowsh[r];
-            } else {
-                // 14 elements = 7 words; the middle row is 8-byte aligned, the outer two are not
+            } else if constexpr (S == 2) {
+                // 14 elements = 7 aligned words; input row 2y (r = 1) is 8-byte aligned, its
+                // neighbours are not
                 if (r == 1) {
                     lds64(a, xw[r][0], xw[r][1]);
                     lds64(a + 8, xw[r][2], xw[r][3]);
@@ -278,6 +289,9 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                     lds64(a + 12, xw[r][3], xw[r][4]);
                     lds64(a + 20, xw[r][5], xw[r][6]);
                 }
+            } else {
+#pragma unroll
+                for (int q = 0; q < NW; ++q) xw[r][q] = lds32(a + 4u * q);
             }
         }
         // ---- the plane's channel filter
@@ -293,7 +307,7 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                 c[4] = lds32(ca + 16);
             }
         }
-        // ---- 57 taps (the 6 that fall left or right of the plane are not emitted), tap-major
+        // ---- the taps (those that fall left or right of the plane are not emitted), tap-major
         float acc[OW];
 #pragma unroll
         for (int p = 0; p < OW; ++p) acc[p] = 0.f;
@@ -313,8 +327,9 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                 }
             }
         }
-        // ---- store 7 results: three words and one half, arranged by the row's word parity
-        {
+        // ---- store the row
+        if constexpr (OSHIFT) {
+            // 7 results: three words and one half, arranged by the row's word parity
             const uint32_t w0 = Word<T>::put(acc[0], acc[1]), w1 = Word<T>::put(acc[2], acc[3]);
             const uint32_t w2 = Word<T>::put(acc[4], acc[5]), w3 = Word<T>::put(acc[6], 0.f);
             const uint32_t v0 = __funnelshift_r(w0, w1, osh), v1 = __funnelshift_r(w1, w2, osh);
@@ -324,8 +339,11 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             stg32(pw + 4, v1);
             stg32(pw + 8, v2);
             stg16(outp + (opar ? 0 : 12), opar ? w0 : w3);
+        } else {
+#pragma unroll
+            for (int q = 0; q < NSW; ++q) stg32(outp + 4 * q, Word<T>::put(acc[2 * q], acc[2 * q + 1]));
         }
-        outp += kRowChunk * OW * OW * 2;
+        outp += CH * OW * OW * 2;
         __syncwarp();
         if (lane == 0) mbar_arrive(WBAR_EMPTY(slot));
         if (++slot == NST) { slot = 0; ph ^= 1u; }
@@ -350,16 +368,17 @@ struct RowArgs {
     int device;
 };
 
-template <typename T, int S, int MODE>
+template <typename T, int S, int OW, int MODE>
 int row_launch(const RowArgs& a, cudaStream_t stream) {
     const Problem& p = a.p;
-    constexpr int W = 7 * S;
+    constexpr int W = OW * S;
+    constexpr int kRowChunk = kRowCompute / OW;
     RowPlan pl;
     pl.in = a.in; pl.cf = a.cf; pl.sf = a.sf; pl.out = a.out;
     pl.chunks_per_sample = p.C / kRowChunk;
     pl.total_chunks = (long long)p.B * pl.chunks_per_sample;
     pl.chunk_bytes = (uint32_t)(kRowChunk * W * W * 2);
-    pl.sf_bytes = 9u * 49u * 2u;
+    pl.sf_bytes = (uint32_t)(9 * OW * OW * 2);
     pl.sf_total = (unsigned long long)p.B * pl.sf_bytes;
     pl.off_zero = round_up(8u * (3 * kRowMaxSlots + 4), 16);
     pl.off_sf = round_up(pl.off_zero + 64u, 128);
@@ -379,7 +398,7 @@ int row_launch(const RowArgs& a, cudaStream_t stream) {
     pl.wait_cycles = kWaitCycles;
     const uint32_t smem = pl.off_stage0 + (uint32_t)slots * pl.stage_stride;
     const int grid = (int)(pl.total_chunks < a.sm_count ? pl.total_chunks : a.sm_count);
-    auto kern = row_kernel<T, S, MODE>;
+    auto kern = row_kernel<T, S, OW, MODE>;
     static std::atomic<unsigned long long> opted_in{0};
     const unsigned long long bit = 1ull << (a.device & 63);
     if (!(opted_in.load(std::memory_order_acquire) & bit)) {
@@ -395,8 +414,9 @@ inline bool row_applicable(const RowArgs& a) {
     const Problem& p = a.p;
     if (p.dtype != DDF_B200_F16 && p.dtype != DDF_B200_BF16) return false;
     if (p.k != 3 || p.d != 1 || (p.s != 1 && p.s != 2) || p.sf_norm) return false;
-    if (p.OH != 7 || p.OW != 7 || p.H != 7 * p.s || p.W != 7 * p.s) return false;
-    if (p.C % kRowChunk != 0) return false;
+    if (p.OH != p.OW || (p.OW != 7 && !(p.OW == 14 && p.s == 1))) return false;
+    if (p.H != p.OH * p.s || p.W != p.OW * p.s) return false;
+    if (p.C % (kRowCompute / p.OW) != 0) return false;
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
     return al16(a.in) && al16(a.cf) && al16(a.sf) && al16(a.out);
 }

@@ -78,6 +78,8 @@ STREAM = [
     (2400, 64, 7, 7, 3, 1, 1),   # row kernel: more chunks per CTA than ring slots
     (3, 192, 14, 14, 3, 1, 2),   # row kernel, stride 2
     (1100, 64, 14, 14, 3, 1, 2), # row kernel, stride 2: ring slots reused
+    (5, 96, 14, 14, 3, 1, 1),    # row kernel, 14-pixel rows: three chunks per sample
+    (2100, 32, 14, 14, 3, 1, 1), # row kernel, 14-pixel rows: ring slots and filter buffers reused
 ]
 
 
