@@ -46,7 +46,7 @@ struct RowPlan {
     long long total_chunks;   // B * C / planes per chunk
     uint32_t chunk_bytes;     // one chunk of input planes
     uint32_t sf_bytes;        // 9 * OW * OW * 2
-    unsigned long long sf_total;
+    unsigned long long sf_total, cf_total;
     uint32_t off_zero, off_sf, sf_stride, off_stage0, stage_stride, off_rawcf, off_conv;
     int* fault;
     long long wait_cycles;
@@ -64,19 +64,28 @@ __device__ __forceinline__ void stg16(void* p, uint32_t v) {
     asm volatile("st.global.b16 [%0], %1;" ::"l"(p), "h"((uint16_t)v) : "memory");
 }
 
-template <typename T, int S, int OW, int MODE>
+// NSEG = 1: a thread owns a whole output row (OW = 7 or 14).  NSEG > 1: a row is cut into NSEG
+// segments of 14 pixels (stride 1) or 7 pixels (stride 2), one per thread; a thread's input
+// window then starts two elements left of its segment's first input element (a word
+// boundary) and, at stride 1, ends two elements right of the last one.  The window's first
+// word of a row's first segment and last word of its last segment are ANDed with per-thread
+// constant masks (true zero padding, as in the plane-ring kernel).
+template <typename T, int S, int OW, int NSEG, int MODE>
 __global__ void __launch_bounds__(kRowThreads, 1)
 row_kernel(const __grid_constant__ RowPlan pl) {
     constexpr int K = 3, KK = 9;
-    constexpr int CH = kRowCompute / OW;            // planes per chunk
+    constexpr int SEG = OW / NSEG;                  // output pixels per thread
+    constexpr int TPP = OW * NSEG;                  // threads per plane
+    constexpr int CH = kRowCompute / TPP;           // planes per chunk
     constexpr int W = OW * S;                       // input row length in elements
     constexpr int PLANE = W * W * 2;                // input plane bytes
     constexpr bool XSHIFT = W % 2 != 0;             // input rows start on odd elements: funnel shifts
-    constexpr bool OSHIFT = OW % 2 != 0;            // the same for output and spatial-filter rows
-    constexpr int NW = (W + 1) / 2;                 // words of an input row a thread holds
-    constexpr int NSW = (OW + 1) / 2;               // words of a spatial-filter / output row
+    constexpr bool OSHIFT = SEG % 2 != 0;           // the same for a thread's output and spatial-filter run
+    constexpr int NW = NSEG > 1 ? (S == 1 ? SEG / 2 + 2 : SEG + 1) : (W + 1) / 2;   // words of an input row a thread holds
+    constexpr int NSW = (SEG + 1) / 2;              // words of a thread's spatial-filter / output row
     static_assert(S == 1 || S == 2, "stride 1 or 2");
-    static_assert(W == 7 || W == 14, "input rows of 7 or 14 elements");
+    static_assert(NSEG == 1 ? (W == 7 || W == 14) : (S == 1 ? SEG == 14 : SEG == 7), "row or segment geometry");
+    static_assert(kRowCompute % TPP == 0, "whole planes per chunk");
     static_assert(sizeof(T) == 2, "2-byte element types only");
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -142,12 +151,15 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             if (--left_in_sample == 0) ++b;
             if (round > 0) ok = mbar_wait_for(WBAR_EMPTY(slot), (uint32_t)((round - 1) & 1), pl.wait_cycles);
             if (!ok) break;
-            const uint32_t cfb = (uint32_t)(CH * KK * 2);
-            mbar_arrive_expect_tx(WBAR_FULL(slot), pl.chunk_bytes + cfb);
-            bulk_g2s(WSTAGE(slot), (const char*)pl.in + (unsigned long long)g * pl.chunk_bytes, pl.chunk_bytes,
+            // the chunk's planes (a multiple of 16 bytes from a 16-byte aligned start) and their
+            // channel filters (any byte range: aligned superset, clamped to the tensor's end)
+            constexpr unsigned long long cfb = (unsigned long long)(CH * KK * 2);
+            const Span sc = span_prepare(WSTAGE(slot) + pl.off_rawcf, pl.cf, (unsigned long long)g * cfb,
+                                         (unsigned long long)(g + 1) * cfb, pl.cf_total);
+            mbar_arrive_expect_tx(WBAR_FULL(slot), pl.chunk_bytes + sc.bytes);
+            bulk_g2s(WSTAGE(slot) + 16u, (const char*)pl.in + (unsigned long long)g * pl.chunk_bytes, pl.chunk_bytes,
                      WBAR_FULL(slot));
-            bulk_g2s(WSTAGE(slot) + pl.off_rawcf, (const char*)pl.cf + (unsigned long long)g * cfb, cfb,
-                     WBAR_FULL(slot));
+            span_issue(sc, WBAR_FULL(slot));
             issued = i + 1;
             if (++slot == NST) { slot = 0; ++round; }
         }
@@ -172,7 +184,8 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                 atomicCAS(pl.fault, 0, (int)kFaultConsumerFull);
                 return;
             }
-            const uint32_t src = WSTAGE(slot) + pl.off_rawcf;
+            const uint32_t src = WSTAGE(slot) + pl.off_rawcf +
+                                 (uint32_t)(((unsigned long long)(chunk_lo + i) * (CH * KK * 2)) & 15ull);
             const uint32_t dst = WSTAGE(slot) + pl.off_conv;
 #pragma unroll 3
             for (int e = lane; e < CH * KK; e += 32) {
@@ -189,29 +202,38 @@ row_kernel(const __grid_constant__ RowPlan pl) {
     }
 
     // ------------------------------------------------------------------- compute warps
-    const int j = tid / OW, y = tid - OW * j;   // plane within the chunk, output row
-    // Input rows of this thread relative to its plane: byte offset of the aligned word the
-    // row is read from, funnel shift that brings element 0 to the low half of word 0, and
-    // whether the row lies outside the plane.
+    // plane within the chunk, output row, segment of the row
+    const int j = tid / TPP, y = (tid - TPP * j) / NSEG, g = tid - TPP * j - NSEG * y;
+    // Input rows of this thread relative to the chunk's first plane: byte offset of the aligned
+    // word its window starts at, funnel shift that brings the window's element 0 to the low half
+    // of word 0, and whether the row lies outside the plane.
     uint32_t rowoff[K], rowsh[K];
     bool rowout[K];
 #pragma unroll
     for (int r = 0; r < K; ++r) {
         const int iy = y * S - 1 + r;
         rowout[r] = iy < 0 || iy >= W;
-        const uint32_t a = (uint32_t)(j * PLANE + iy * W * 2);   // (wraps for iy < 0: unused then)
+        // (wraps for iy < 0: unused then)
+        const uint32_t a = 16u + (uint32_t)(j * PLANE + iy * W * 2 + (NSEG > 1 ? (g * SEG * S - 2) * 2 : 0));
         rowoff[r] = XSHIFT ? (a & ~3u) : a;
         rowsh[r] = XSHIFT ? (a & 2u) * 8u : 0u;
     }
+    // masks of the window's first / last word (segments only)
+    uint32_t lmask = (NSEG > 1 && g == 0) ? 0u : 0xffffffffu;
+    uint32_t rmask = (NSEG > 1 && S == 1 && g == NSEG - 1) ? 0u : 0xffffffffu;
+    if constexpr (NSEG > 1) {
+        asm volatile("" : "+r"(lmask));
+        asm volatile("" : "+r"(rmask));
+    }
     const uint32_t zaddr = sbase + pl.off_zero + (S == 2 ? 4u : 0u);   // same alignment class as the rows it replaces
     const uint32_t cfoff = pl.off_conv + (uint32_t)(j * kRowCFP);
-    // output row: OW elements at element offset plane * OW * OW + OW * y; for odd OW its word
-    // parity is a thread constant (a chunk starts on an even plane)
-    const uint32_t opar = OSHIFT ? (uint32_t)((j + y) & 1) : 0u;
+    // output: SEG elements at element offset plane * OW * OW + OW * y + SEG * g; for odd SEG its word
+    // parity is a thread constant (a chunk starts on an even element)
+    const uint32_t opar = OSHIFT ? (uint32_t)((j * OW * OW + y * OW + g * SEG) & 1) : 0u;
     const uint32_t osh = opar * 16u;
     char* outp = reinterpret_cast<char*>(pl.out) +
                  ((unsigned long long)chunk_lo * CH + (unsigned long long)j) * (OW * OW * 2) +
-                 (unsigned long long)(y * OW * 2);
+                 (unsigned long long)((y * OW + g * SEG) * 2);
 
     uint32_t sfw[KK][NSW];
 #pragma unroll
@@ -240,7 +262,8 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                 return;
             }
             const uint32_t sfs = sbase + pl.off_sf + (uint32_t)buf * pl.sf_stride +
-                                 (uint32_t)(((unsigned long long)b * pl.sf_bytes) & 15ull) + (uint32_t)(y * OW * 2);
+                                 (uint32_t)(((unsigned long long)b * pl.sf_bytes) & 15ull) +
+                                 (uint32_t)((y * OW + g * SEG) * 2);
 #pragma unroll
             for (int t = 0; t < KK; ++t) {
                 const uint32_t a = sfs + (uint32_t)(t * OW * OW * 2);
@@ -275,7 +298,7 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                 xw[r][1] = __funnelshift_r(w1, w2, rowsh[r]);
                 xw[r][2] = __funnelshift_r(w2, w3, rowsh[r]);
                 xw[r][3] = w3 >> rowsh[r];
-            } else if constexpr (S == 2) {
+            } else if constexpr (S == 2 && NSEG == 1) {
                 // 14 elements = 7 aligned words; input row 2y (r = 1) is 8-byte aligned, its
                 // neighbours are not
                 if (r == 1) {
@@ -292,6 +315,10 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             } else {
 #pragma unroll
                 for (int q = 0; q < NW; ++q) xw[r][q] = lds32(a + 4u * q);
+                if constexpr (NSEG > 1) {
+                    xw[r][0] &= lmask;
+                    if constexpr (S == 1) xw[r][NW - 1] &= rmask;
+                }
             }
         }
         // ---- the plane's channel filter
@@ -308,16 +335,18 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             }
         }
         // ---- the taps (those that fall left or right of the plane are not emitted), tap-major
-        float acc[OW];
+        float acc[SEG];
 #pragma unroll
-        for (int p = 0; p < OW; ++p) acc[p] = 0.f;
+        for (int p = 0; p < SEG; ++p) acc[p] = 0.f;
 #pragma unroll
         for (int t = 0; t < KK; ++t) {
             const int ti = t / K, tj = t % K;
 #pragma unroll
-            for (int p = 0; p < OW; ++p) {
-                const int e = p * S + tj - 1;   // element of the input row
-                if (e < 0 || e >= W) continue;
+            for (int p = 0; p < SEG; ++p) {
+                // element of the thread's window: whole rows start at the row's element 0 and
+                // drop the taps outside it; segments start two elements left of the segment
+                const int e = NSEG > 1 ? p * S + tj + 1 : p * S + tj - 1;
+                if (NSEG == 1 && (e < 0 || e >= W)) continue;
                 if constexpr (MODE == DDF_B200_MUL) {
                     const float yv = Mix<T>::fmaw(e & 1, p & 1, xw[ti][e >> 1], sfw[t][p >> 1], 0.f);
                     acc[p] = fmaf(yv, __uint_as_float(c[t]), acc[p]);
@@ -368,11 +397,11 @@ struct RowArgs {
     int device;
 };
 
-template <typename T, int S, int OW, int MODE>
+template <typename T, int S, int OW, int NSEG, int MODE>
 int row_launch(const RowArgs& a, cudaStream_t stream) {
     const Problem& p = a.p;
     constexpr int W = OW * S;
-    constexpr int kRowChunk = kRowCompute / OW;
+    constexpr int kRowChunk = kRowCompute / (OW * NSEG);
     RowPlan pl;
     pl.in = a.in; pl.cf = a.cf; pl.sf = a.sf; pl.out = a.out;
     pl.chunks_per_sample = p.C / kRowChunk;
@@ -380,12 +409,15 @@ int row_launch(const RowArgs& a, cudaStream_t stream) {
     pl.chunk_bytes = (uint32_t)(kRowChunk * W * W * 2);
     pl.sf_bytes = (uint32_t)(9 * OW * OW * 2);
     pl.sf_total = (unsigned long long)p.B * pl.sf_bytes;
+    pl.cf_total = (unsigned long long)p.B * p.C * 18ull;
     pl.off_zero = round_up(8u * (3 * kRowMaxSlots + 4), 16);
     pl.off_sf = round_up(pl.off_zero + 64u, 128);
     pl.sf_stride = round_up(pl.sf_bytes + 48u, 128);
     pl.off_stage0 = pl.off_sf + 2u * pl.sf_stride;
-    pl.off_rawcf = round_up(pl.chunk_bytes + 16u, 16);      // a row's last word load may run 14 bytes over
-    pl.off_conv = round_up(pl.off_rawcf + (uint32_t)(kRowChunk * 9 * 2), 16);
+    // [16 bytes: a first segment's window starts 4 bytes early][planes][16 bytes: a last row's or
+    // last segment's window runs up to 14 bytes over][raw channel filters + alignment slack]
+    pl.off_rawcf = round_up(16u + pl.chunk_bytes + 16u, 16);
+    pl.off_conv = round_up(pl.off_rawcf + (uint32_t)(kRowChunk * 9 * 2) + 32u, 16);
     pl.stage_stride = round_up(pl.off_conv + (uint32_t)(kRowChunk * kRowCFP), 128);
     const long long share = (pl.total_chunks + a.sm_count - 1) / a.sm_count;
     int slots = (int)((kSmemBudget - pl.off_stage0) / pl.stage_stride);
@@ -398,7 +430,7 @@ int row_launch(const RowArgs& a, cudaStream_t stream) {
     pl.wait_cycles = kWaitCycles;
     const uint32_t smem = pl.off_stage0 + (uint32_t)slots * pl.stage_stride;
     const int grid = (int)(pl.total_chunks < a.sm_count ? pl.total_chunks : a.sm_count);
-    auto kern = row_kernel<T, S, OW, MODE>;
+    auto kern = row_kernel<T, S, OW, NSEG, MODE>;
     static std::atomic<unsigned long long> opted_in{0};
     const unsigned long long bit = 1ull << (a.device & 63);
     if (!(opted_in.load(std::memory_order_acquire) & bit)) {
@@ -414,9 +446,13 @@ inline bool row_applicable(const RowArgs& a) {
     const Problem& p = a.p;
     if (p.dtype != DDF_B200_F16 && p.dtype != DDF_B200_BF16) return false;
     if (p.k != 3 || p.d != 1 || (p.s != 1 && p.s != 2) || p.sf_norm) return false;
-    if (p.OH != p.OW || (p.OW != 7 && !(p.OW == 14 && p.s == 1))) return false;
-    if (p.H != p.OH * p.s || p.W != p.OW * p.s) return false;
-    if (p.C % (kRowCompute / p.OW) != 0) return false;
+    if (p.OH != p.OW || p.H != p.OH * p.s || p.W != p.OW * p.s) return false;
+    int tpp;   // threads per plane
+    if (p.OW == 7) tpp = 7;
+    else if (p.s == 1 && (p.OW == 14 || p.OW == 28 || p.OW == 56)) tpp = p.OW * (p.OW / 14);
+    else if (p.s == 2 && (p.OW == 14 || p.OW == 28)) tpp = p.OW * (p.OW / 7);
+    else return false;
+    if (p.C % (kRowCompute / tpp) != 0) return false;
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
     return al16(a.in) && al16(a.cf) && al16(a.sf) && al16(a.out);
 }

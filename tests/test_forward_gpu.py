@@ -80,6 +80,10 @@ STREAM = [
     (1100, 64, 14, 14, 3, 1, 2), # row kernel, stride 2: ring slots reused
     (5, 96, 14, 14, 3, 1, 1),    # row kernel, 14-pixel rows: three chunks per sample
     (2100, 32, 14, 14, 3, 1, 1), # row kernel, 14-pixel rows: ring slots and filter buffers reused
+    (300, 8, 28, 28, 3, 1, 1),   # row kernel, two 14-pixel segments per row, one chunk per sample
+    (40, 6, 56, 56, 3, 1, 1),    # row kernel, four segments per row, three chunks per sample
+    (600, 32, 28, 28, 3, 1, 2),  # row kernel, stride 2, two 7-pixel segments per row: slots reused
+    (320, 16, 56, 56, 3, 1, 2),  # row kernel, stride 2, four segments per row: slots reused
 ]
 
 
