@@ -70,13 +70,16 @@ __device__ __forceinline__ void stg16(void* p, uint32_t v) {
 // boundary) and, at stride 1, ends two elements right of the last one.  The window's first
 // word of a row's first segment and last word of its last segment are ANDed with per-thread
 // constant masks (true zero padding, as in the plane-ring kernel).
-template <typename T, int S, int OW, int NSEG, int MODE>
+// TPC: tasks (planes) a thread does per chunk; 2 halves the per-chunk barrier traffic where a
+// CTA's share is many chunks.
+template <typename T, int S, int OW, int NSEG, int TPC, int MODE>
 __global__ void __launch_bounds__(kRowThreads, 1)
 row_kernel(const __grid_constant__ RowPlan pl) {
     constexpr int K = 3, KK = 9;
     constexpr int SEG = OW / NSEG;                  // output pixels per thread
     constexpr int TPP = OW * NSEG;                  // threads per plane
-    constexpr int CH = kRowCompute / TPP;           // planes per chunk
+    constexpr int CHT = kRowCompute / TPP;          // planes the compute threads cover at once
+    constexpr int CH = CHT * TPC;                   // planes per chunk
     constexpr int W = OW * S;                       // input row length in elements
     constexpr int PLANE = W * W * 2;                // input plane bytes
     constexpr bool XSHIFT = W % 2 != 0;             // input rows start on odd elements: funnel shifts
@@ -286,91 +289,109 @@ row_kernel(const __grid_constant__ RowPlan pl) {
         }
         if (--left_in_sample == 0) ++b;
 
-        const uint32_t st = WSTAGE(slot);
-        // ---- the plane's input rows
-        uint32_t xw[K][NW];
+#pragma unroll 1
+        for (int u = 0; u < TPC; ++u) {
+            // task u of the chunk: plane u * CHT + j
+            const uint32_t st = WSTAGE(slot) + (uint32_t)(u * CHT * PLANE);
+            const uint32_t ca0 = WSTAGE(slot) + cfoff + (uint32_t)(u * CHT * kRowCFP);
+            char* op = outp + u * (CHT * OW * OW * 2);
+            // ---- the plane's input rows
+            uint32_t xw[K][NW];
 #pragma unroll
-        for (int r = 0; r < K; ++r) {
-            const uint32_t a = rowout[r] ? zaddr : st + rowoff[r];
-            if constexpr (XSHIFT) {
-                const uint32_t w0 = lds32(a), w1 = lds32(a + 4), w2 = lds32(a + 8), w3 = lds32(a + 12);
-                xw[r][0] = __funnelshift_r(w0, w1, rowsh[r]);
-                xw[r][1] = __funnelshift_r(w1, w2, rowsh[r]);
-                xw[r][2] = __funnelshift_r(w2, w3, rowsh[r]);
-                xw[r][3] = w3 >> rowsh[r];
-            } else if constexpr (S == 2 && NSEG == 1) {
-                // 14 elements = 7 aligned words; input row 2y (r = 1) is 8-byte aligned, its
-                // neighbours are not
-                if (r == 1) {
-                    lds64(a, xw[r][0], xw[r][1]);
-                    lds64(a + 8, xw[r][2], xw[r][3]);
-                    lds64(a + 16, xw[r][4], xw[r][5]);
-                    xw[r][6] = lds32(a + 24);
+            for (int r = 0; r < K; ++r) {
+                const uint32_t a = rowout[r] ? zaddr : st + rowoff[r];
+                if constexpr (XSHIFT) {
+                    const uint32_t w0 = lds32(a), w1 = lds32(a + 4), w2 = lds32(a + 8), w3 = lds32(a + 12);
+                    xw[r][0] = __funnelshift_r(w0, w1, rowsh[r]);
+                    xw[r][1] = __funnelshift_r(w1, w2, rowsh[r]);
+                    xw[r][2] = __funnelshift_r(w2, w3, rowsh[r]);
+                    xw[r][3] = w3 >> rowsh[r];
+                } else if constexpr (S == 2 && NSEG == 1) {
+                    // 14 elements = 7 aligned words; input row 2y (r = 1) is 8-byte aligned, its
+                    // neighbours are not
+                    if (r == 1) {
+                        lds64(a, xw[r][0], xw[r][1]);
+                        lds64(a + 8, xw[r][2], xw[r][3]);
+                        lds64(a + 16, xw[r][4], xw[r][5]);
+                        xw[r][6] = lds32(a + 24);
+                    } else {
+                        xw[r][0] = lds32(a);
+                        lds64(a + 4, xw[r][1], xw[r][2]);
+                        lds64(a + 12, xw[r][3], xw[r][4]);
+                        lds64(a + 20, xw[r][5], xw[r][6]);
+                    }
                 } else {
-                    xw[r][0] = lds32(a);
-                    lds64(a + 4, xw[r][1], xw[r][2]);
-                    lds64(a + 12, xw[r][3], xw[r][4]);
-                    lds64(a + 20, xw[r][5], xw[r][6]);
-                }
-            } else {
 #pragma unroll
-                for (int q = 0; q < NW; ++q) xw[r][q] = lds32(a + 4u * q);
-                if constexpr (NSEG > 1) {
-                    xw[r][0] &= lmask;
-                    if constexpr (S == 1) xw[r][NW - 1] &= rmask;
+                    for (int q = 0; q < NW; ++q) xw[r][q] = lds32(a + 4u * q);
+                    if constexpr (NSEG > 1) {
+                        xw[r][0] &= lmask;
+                        if constexpr (S == 1) xw[r][NW - 1] &= rmask;
+                    }
                 }
             }
-        }
-        // ---- the plane's channel filter
-        uint32_t c[12];
-        {
-            const uint32_t ca = st + cfoff;
-            if constexpr (MODE == DDF_B200_MUL) {
-                lds128(ca, c[0], c[1], c[2], c[3]);
-                lds128(ca + 16, c[4], c[5], c[6], c[7]);
-                c[8] = lds32(ca + 32);
-            } else {
-                lds128(ca, c[0], c[1], c[2], c[3]);
-                c[4] = lds32(ca + 16);
-            }
-        }
-        // ---- the taps (those that fall left or right of the plane are not emitted), tap-major
-        float acc[SEG];
-#pragma unroll
-        for (int p = 0; p < SEG; ++p) acc[p] = 0.f;
-#pragma unroll
-        for (int t = 0; t < KK; ++t) {
-            const int ti = t / K, tj = t % K;
-#pragma unroll
-            for (int p = 0; p < SEG; ++p) {
-                // element of the thread's window: whole rows start at the row's element 0 and
-                // drop the taps outside it; segments start two elements left of the segment
-                const int e = NSEG > 1 ? p * S + tj + 1 : p * S + tj - 1;
-                if (NSEG == 1 && (e < 0 || e >= W)) continue;
+            // ---- the plane's channel filter
+            uint32_t c[12];
+            {
+                const uint32_t ca = ca0;
                 if constexpr (MODE == DDF_B200_MUL) {
-                    const float yv = Mix<T>::fmaw(e & 1, p & 1, xw[ti][e >> 1], sfw[t][p >> 1], 0.f);
-                    acc[p] = fmaf(yv, __uint_as_float(c[t]), acc[p]);
+                    lds128(ca, c[0], c[1], c[2], c[3]);
+                    lds128(ca + 16, c[4], c[5], c[6], c[7]);
+                    c[8] = lds32(ca + 32);
                 } else {
-                    acc[p] = Mix<T>::fmaw(e & 1, p & 1, xw[ti][e >> 1], sfw[t][p >> 1], acc[p]);
-                    acc[p] = Mix<T>::fmaw(e & 1, t & 1, xw[ti][e >> 1], c[t >> 1], acc[p]);
+                    lds128(ca, c[0], c[1], c[2], c[3]);
+                    c[4] = lds32(ca + 16);
                 }
             }
-        }
-        // ---- store the row
-        if constexpr (OSHIFT) {
-            // 7 results: three words and one half, arranged by the row's word parity
-            const uint32_t w0 = Word<T>::put(acc[0], acc[1]), w1 = Word<T>::put(acc[2], acc[3]);
-            const uint32_t w2 = Word<T>::put(acc[4], acc[5]), w3 = Word<T>::put(acc[6], 0.f);
-            const uint32_t v0 = __funnelshift_r(w0, w1, osh), v1 = __funnelshift_r(w1, w2, osh);
-            const uint32_t v2 = __funnelshift_r(w2, w3, osh);
-            char* pw = outp + 2u * opar;
-            stg32(pw, v0);
-            stg32(pw + 4, v1);
-            stg32(pw + 8, v2);
-            stg16(outp + (opar ? 0 : 12), opar ? w0 : w3);
-        } else {
+            // ---- the taps (those that fall left or right of the plane are not emitted), tap-major
+            float acc[SEG];
 #pragma unroll
-            for (int q = 0; q < NSW; ++q) stg32(outp + 4 * q, Word<T>::put(acc[2 * q], acc[2 * q + 1]));
+            for (int p = 0; p < SEG; ++p) acc[p] = 0.f;
+#pragma unroll
+            for (int t = 0; t < KK; ++t) {
+                const int ti = t / K, tj = t % K;
+                // element of the thread's window for pixel p: whole rows start at the row's element 0
+                // and drop the taps outside it; segments start two elements left of the segment
+                if constexpr (MODE == DDF_B200_MUL) {
+                    // the exact products of the tap first, then the FMAs that share c[t]
+                    float yv[SEG];
+#pragma unroll
+                    for (int p = 0; p < SEG; ++p) {
+                        const int e = NSEG > 1 ? p * S + tj + 1 : p * S + tj - 1;
+                        if (NSEG == 1 && (e < 0 || e >= W)) continue;
+                        yv[p] = Mix<T>::fmaw(e & 1, p & 1, xw[ti][e >> 1], sfw[t][p >> 1], 0.f);
+                    }
+#pragma unroll
+                    for (int p = 0; p < SEG; ++p) {
+                        const int e = NSEG > 1 ? p * S + tj + 1 : p * S + tj - 1;
+                        if (NSEG == 1 && (e < 0 || e >= W)) continue;
+                        acc[p] = fmaf(yv[p], __uint_as_float(c[t]), acc[p]);
+                    }
+                } else {
+#pragma unroll
+                    for (int p = 0; p < SEG; ++p) {
+                        const int e = NSEG > 1 ? p * S + tj + 1 : p * S + tj - 1;
+                        if (NSEG == 1 && (e < 0 || e >= W)) continue;
+                        acc[p] = Mix<T>::fmaw(e & 1, p & 1, xw[ti][e >> 1], sfw[t][p >> 1], acc[p]);
+                        acc[p] = Mix<T>::fmaw(e & 1, t & 1, xw[ti][e >> 1], c[t >> 1], acc[p]);
+                    }
+                }
+            }
+            // ---- store the row
+            if constexpr (OSHIFT) {
+                // 7 results: three words and one half, arranged by the row's word parity
+                const uint32_t w0 = Word<T>::put(acc[0], acc[1]), w1 = Word<T>::put(acc[2], acc[3]);
+                const uint32_t w2 = Word<T>::put(acc[4], acc[5]), w3 = Word<T>::put(acc[6], 0.f);
+                const uint32_t v0 = __funnelshift_r(w0, w1, osh), v1 = __funnelshift_r(w1, w2, osh);
+                const uint32_t v2 = __funnelshift_r(w2, w3, osh);
+                char* pw = op + 2u * opar;
+                stg32(pw, v0);
+                stg32(pw + 4, v1);
+                stg32(pw + 8, v2);
+                stg16(op + (opar ? 0 : 12), opar ? w0 : w3);
+            } else {
+#pragma unroll
+                for (int q = 0; q < NSW; ++q) stg32(op + 4 * q, Word<T>::put(acc[2 * q], acc[2 * q + 1]));
+            }
         }
         outp += CH * OW * OW * 2;
         __syncwarp();
@@ -397,11 +418,11 @@ struct RowArgs {
     int device;
 };
 
-template <typename T, int S, int OW, int NSEG, int MODE>
+template <typename T, int S, int OW, int NSEG, int TPC, int MODE>
 int row_launch(const RowArgs& a, cudaStream_t stream) {
     const Problem& p = a.p;
     constexpr int W = OW * S;
-    constexpr int kRowChunk = kRowCompute / (OW * NSEG);
+    constexpr int kRowChunk = TPC * (kRowCompute / (OW * NSEG));
     RowPlan pl;
     pl.in = a.in; pl.cf = a.cf; pl.sf = a.sf; pl.out = a.out;
     pl.chunks_per_sample = p.C / kRowChunk;
@@ -430,7 +451,7 @@ int row_launch(const RowArgs& a, cudaStream_t stream) {
     pl.wait_cycles = kWaitCycles;
     const uint32_t smem = pl.off_stage0 + (uint32_t)slots * pl.stage_stride;
     const int grid = (int)(pl.total_chunks < a.sm_count ? pl.total_chunks : a.sm_count);
-    auto kern = row_kernel<T, S, OW, NSEG, MODE>;
+    auto kern = row_kernel<T, S, OW, NSEG, TPC, MODE>;
     static std::atomic<unsigned long long> opted_in{0};
     const unsigned long long bit = 1ull << (a.device & 63);
     if (!(opted_in.load(std::memory_order_acquire) & bit)) {
@@ -441,20 +462,23 @@ int row_launch(const RowArgs& a, cudaStream_t stream) {
     return (int)launch_overlapped(kern, dim3((unsigned)grid), dim3((unsigned)kRowThreads), smem, stream, true, pl);
 }
 
-// The problems the row kernel is built for.
-inline bool row_applicable(const RowArgs& a) {
+// The problems the row kernel is built for: returns the number of planes its compute threads
+// cover at once (a chunk is one or two of those; C must be a multiple of the chunk), 0 if the
+// problem is not covered.
+inline int row_planes_at_once(const RowArgs& a) {
     const Problem& p = a.p;
-    if (p.dtype != DDF_B200_F16 && p.dtype != DDF_B200_BF16) return false;
-    if (p.k != 3 || p.d != 1 || (p.s != 1 && p.s != 2) || p.sf_norm) return false;
-    if (p.OH != p.OW || p.H != p.OH * p.s || p.W != p.OW * p.s) return false;
+    if (p.dtype != DDF_B200_F16 && p.dtype != DDF_B200_BF16) return 0;
+    if (p.k != 3 || p.d != 1 || (p.s != 1 && p.s != 2) || p.sf_norm) return 0;
+    if (p.OH != p.OW || p.H != p.OH * p.s || p.W != p.OW * p.s) return 0;
     int tpp;   // threads per plane
     if (p.OW == 7) tpp = 7;
     else if (p.s == 1 && (p.OW == 14 || p.OW == 28 || p.OW == 56)) tpp = p.OW * (p.OW / 14);
     else if (p.s == 2 && (p.OW == 14 || p.OW == 28)) tpp = p.OW * (p.OW / 7);
-    else return false;
-    if (p.C % (kRowCompute / tpp) != 0) return false;
+    else return 0;
+    const int cht = kRowCompute / tpp;
+    if (p.C % cht != 0) return 0;
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
-    return al16(a.in) && al16(a.cf) && al16(a.sf) && al16(a.out);
+    return (al16(a.in) && al16(a.cf) && al16(a.sf) && al16(a.out)) ? cht : 0;
 }
 
 // Defined per element type in row_inst_<type>.cu.
