@@ -276,7 +276,7 @@ static int forward_impl(const Problem& p, const void* x, const void* cf, const v
         if (want) {
             RingArgs ra{x, cf, sf, out, p, false, di->sm_count, di->fault, di->index,
                         true, 0, 0u};
-            RowArgs wa{x, cf, sf, out, p, di->sm_count, di->fault, di->index};
+            RowArgs wa{x, cf, sf, out, p, false, di->sm_count, di->fault, di->index};
             rc = run_row(wa, st);
             if (rc != kNotHandled) return rc;
             rc = run_ring(ra, st);
@@ -434,9 +434,15 @@ int ddf_b200_backward(const void* go, const void* x, const void* cf, const void*
         if (allow_stream && want) {
             RingArgs ra{go, cf, sf, gx, p, true, di->sm_count, di->fault, di->index,
                         true, 0, 0u};
-            rc = run_ring(ra, st);
+            RowArgs wa{go, cf, sf, gx, p, true, di->sm_count, di->fault, di->index};
+            rc = run_row(wa, st);
             if (rc == 0) done = true;
             else if (rc != kNotHandled) return rc;
+            if (!done) {
+                rc = run_ring(ra, st);
+                if (rc == 0) done = true;
+                else if (rc != kNotHandled) return rc;
+            }
             const int P = done ? 0 : stream_pixels(p, true);
             if (P > 0) {
                 StreamArgs a{go, cf, sf, gx, p, true, di->sm_count, di->fault, P, di->index, 2, 0, p.k == 3};

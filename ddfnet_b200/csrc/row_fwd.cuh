@@ -72,7 +72,10 @@ __device__ __forceinline__ void stg16(void* p, uint32_t v) {
 // constant masks (true zero padding, as in the plane-ring kernel).
 // TPC: tasks (planes) a thread does per chunk; 2 halves the per-chunk barrier traffic where a
 // CTA's share is many chunks.
-template <typename T, int S, int OW, int NSEG, int TPC, int MODE>
+// BWDX: grad-x at stride 1 -- the same kernel over go with the channel filter's taps mirrored
+// and, for window tap (i, j), the spatial filter of the mirrored tap at the neighbouring
+// pixel the product came from.
+template <typename T, int S, int OW, int NSEG, int TPC, int MODE, bool BWDX>
 __global__ void __launch_bounds__(kRowThreads, 1)
 row_kernel(const __grid_constant__ RowPlan pl) {
     constexpr int K = 3, KK = 9;
@@ -89,6 +92,7 @@ row_kernel(const __grid_constant__ RowPlan pl) {
     static_assert(S == 1 || S == 2, "stride 1 or 2");
     static_assert(NSEG == 1 ? (W == 7 || W == 14) : (S == 1 ? SEG == 14 : SEG == 7), "row or segment geometry");
     static_assert(kRowCompute % TPP == 0, "whole planes per chunk");
+    static_assert(!BWDX || S == 1, "grad-x at stride 1 only");
     static_assert(sizeof(T) == 2, "2-byte element types only");
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -193,9 +197,10 @@ row_kernel(const __grid_constant__ RowPlan pl) {
 #pragma unroll 3
             for (int e = lane; e < CH * KK; e += 32) {
                 const int u = e / KK, t = e - u * KK;
+                const int tt = BWDX ? KK - 1 - t : t;
                 const uint32_t raw = lds16(src + 2u * (uint32_t)e);
-                if constexpr (MODE == DDF_B200_MUL) sts32(dst + (uint32_t)(u * kRowCFP + 4 * t), Mix<T>::f32_bits(raw));
-                else sts16(dst + (uint32_t)(u * kRowCFP + 2 * t), raw);
+                if constexpr (MODE == DDF_B200_MUL) sts32(dst + (uint32_t)(u * kRowCFP + 4 * tt), Mix<T>::f32_bits(raw));
+                else sts16(dst + (uint32_t)(u * kRowCFP + 2 * tt), raw);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(WBAR_CF(slot));
@@ -269,17 +274,39 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                                  (uint32_t)((y * OW + g * SEG) * 2);
 #pragma unroll
             for (int t = 0; t < KK; ++t) {
-                const uint32_t a = sfs + (uint32_t)(t * OW * OW * 2);
-                if constexpr (OSHIFT) {
-                    const uint32_t aw = a & ~3u, sh = (a & 2u) * 8u;
-                    const uint32_t w0 = lds32(aw), w1 = lds32(aw + 4), w2 = lds32(aw + 8), w3 = lds32(aw + 12);
-                    sfw[t][0] = __funnelshift_r(w0, w1, sh);
-                    sfw[t][1] = __funnelshift_r(w1, w2, sh);
-                    sfw[t][2] = __funnelshift_r(w2, w3, sh);
-                    sfw[t][3] = w3 >> sh;
-                } else {
+                if constexpr (!BWDX) {
+                    const uint32_t a = sfs + (uint32_t)(t * OW * OW * 2);
+                    if constexpr (OSHIFT) {
+                        const uint32_t aw = a & ~3u, sh = (a & 2u) * 8u;
+                        const uint32_t w0 = lds32(aw), w1 = lds32(aw + 4), w2 = lds32(aw + 8), w3 = lds32(aw + 12);
+                        sfw[t][0] = __funnelshift_r(w0, w1, sh);
+                        sfw[t][1] = __funnelshift_r(w1, w2, sh);
+                        sfw[t][2] = __funnelshift_r(w2, w3, sh);
+                        sfw[t][3] = w3 >> sh;
+                    } else {
 #pragma unroll
-                    for (int q = 0; q < NSW; ++q) sfw[t][q] = lds32(a + 4u * q);
+                        for (int q = 0; q < NSW; ++q) sfw[t][q] = lds32(a + 4u * q);
+                    }
+                } else {
+                    // window tap (ti, tj): filter plane KK-1-t, row y + ti - 1, elements
+                    // g*SEG + tj - 1 + p (p = 0..SEG-1); what lies outside the plane is zero
+                    const int ti = t / K, tj = t % K;
+                    const int yy = y + ti - 1;
+                    const uint32_t a = sfs + (uint32_t)(((KK - 1 - t) * OW * OW + (ti - 1) * OW + (tj - 1)) * 2);
+                    const uint32_t aw = a & ~3u, sh = (a & 2u) * 8u;
+                    uint32_t wv[NSW + 1];
+#pragma unroll
+                    for (int q = 0; q <= NSW; ++q) wv[q] = lds32(aw + 4u * q);
+#pragma unroll
+                    for (int q = 0; q < NSW; ++q) sfw[t][q] = __funnelshift_r(wv[q], wv[q + 1], sh);
+                    if (SEG % 2 != 0) sfw[t][NSW - 1] &= 0x0000ffffu;          // the half past the run
+                    if (tj == 0 && g == 0) sfw[t][0] &= 0xffff0000u;           // column -1
+                    if (tj == 2 && g == NSEG - 1)                              // column OW
+                        sfw[t][NSW - 1] &= (SEG % 2 != 0) ? 0u : 0x0000ffffu;
+                    if (yy < 0 || yy >= OW) {
+#pragma unroll
+                        for (int q = 0; q < NSW; ++q) sfw[t][q] = 0u;
+                    }
                 }
             }
             __syncwarp();
@@ -408,17 +435,18 @@ row_kernel(const __grid_constant__ RowPlan pl) {
 
 // ------------------------------------------------------------------------ host side
 struct RowArgs {
-    const void* in;
+    const void* in;   // x for the forward, go for grad-x
     const void* cf;
     const void* sf;
-    void* out;
+    void* out;        // out for the forward, gx for grad-x
     Problem p;
+    bool bwdx;
     int sm_count;
     int* fault;
     int device;
 };
 
-template <typename T, int S, int OW, int NSEG, int TPC, int MODE>
+template <typename T, int S, int OW, int NSEG, int TPC, int MODE, bool BWDX>
 int row_launch(const RowArgs& a, cudaStream_t stream) {
     const Problem& p = a.p;
     constexpr int W = OW * S;
@@ -451,7 +479,7 @@ int row_launch(const RowArgs& a, cudaStream_t stream) {
     pl.wait_cycles = kWaitCycles;
     const uint32_t smem = pl.off_stage0 + (uint32_t)slots * pl.stage_stride;
     const int grid = (int)(pl.total_chunks < a.sm_count ? pl.total_chunks : a.sm_count);
-    auto kern = row_kernel<T, S, OW, NSEG, TPC, MODE>;
+    auto kern = row_kernel<T, S, OW, NSEG, TPC, MODE, BWDX>;
     static std::atomic<unsigned long long> opted_in{0};
     const unsigned long long bit = 1ull << (a.device & 63);
     if (!(opted_in.load(std::memory_order_acquire) & bit)) {
@@ -469,6 +497,7 @@ inline int row_planes_at_once(const RowArgs& a) {
     const Problem& p = a.p;
     if (p.dtype != DDF_B200_F16 && p.dtype != DDF_B200_BF16) return 0;
     if (p.k != 3 || p.d != 1 || (p.s != 1 && p.s != 2) || p.sf_norm) return 0;
+    if (a.bwdx && p.s != 1) return 0;
     if (p.OH != p.OW || p.H != p.OH * p.s || p.W != p.OW * p.s) return 0;
     int tpp;   // threads per plane
     if (p.OW == 7) tpp = 7;

@@ -60,6 +60,9 @@ STREAM = [
     (3, 32, 56, 56, 3, 1, 2),
     (3, 32, 28, 28, 3, 1, 2),
     (2, 24, 20, 24, 3, 1, 1),
+    (300, 8, 28, 28, 3, 1, 1),   # grad-x in the row kernel: a new sample every chunk, filter buffers reused
+    (400, 64, 7, 7, 3, 1, 1),
+    (40, 6, 56, 56, 3, 1, 1),
 ]
 
 
