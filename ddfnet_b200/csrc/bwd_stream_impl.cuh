@@ -566,10 +566,47 @@ gsf_reduce_kernel(const float* __restrict__ scratch, T* __restrict__ gsf, int B,
         // The slots of those CTAs are consecutive: slot j holds n_per_sample floats.
         const int nslot = s_nslot;
         const float* base = scratch + (b + s_c0) * NP * n_per_sample;
+        if ((n_per_sample & 3) == 0 && ((reinterpret_cast<uintptr_t>(scratch) | reinterpret_cast<uintptr_t>(gsf)) & 15u) == 0) {
+            // four elements per thread: 16-byte loads, four slots in flight; the order of the
+            // additions is fixed, so the result does not depend on scheduling
+            const long long n4 = n_per_sample >> 2;
+            for (long long e4 = blockIdx.x * (long long)blockDim.x + threadIdx.x; e4 < n4;
+                 e4 += (long long)gridDim.x * blockDim.x) {
+                float4 acc[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int j0 = 0; j0 < nslot; j0 += 4) {
+                    float4 v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        v[u] = (j0 + u < nslot)
+                                   ? __ldg(reinterpret_cast<const float4*>(base + (long long)(j0 + u) * n_per_sample) + e4)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w;
+                    }
+                }
+                float tot[4];
+                tot[0] = (acc[0].x + acc[1].x) + (acc[2].x + acc[3].x);
+                tot[1] = (acc[0].y + acc[1].y) + (acc[2].y + acc[3].y);
+                tot[2] = (acc[0].z + acc[1].z) + (acc[2].z + acc[3].z);
+                tot[3] = (acc[0].w + acc[1].w) + (acc[2].w + acc[3].w);
+                T* dst = gsf + b * n_per_sample + 4 * e4;
+                if constexpr (sizeof(T) == 4) {
+                    *reinterpret_cast<float4*>(dst) = make_float4(tot[0], tot[1], tot[2], tot[3]);
+                } else if constexpr (sizeof(T) == 2) {
+                    *reinterpret_cast<uint2*>(dst) = make_uint2(Word<T>::put(tot[0], tot[1]), Word<T>::put(tot[2], tot[3]));
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) Elem<T>::store(dst + u, tot[u]);
+                }
+            }
+            continue;
+        }
         for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < n_per_sample;
              e += (long long)gridDim.x * blockDim.x) {
-            // Eight loads in flight per thread; the order of the additions is fixed, so
-            // the result does not depend on scheduling.
+            // Eight loads in flight per thread; fixed order of additions.
             float acc[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) acc[u] = 0.f;
@@ -720,7 +757,11 @@ int bwd_launch(const BwdArgs& a, cudaStream_t stream, int* launches) {
     ++*launches;
     if (a.gsf) {
         const long long n = (long long)a.p.k * a.p.k * a.p.OH * a.p.OW;
-        dim3 grid((unsigned)((n + 255) / 256 < 64 ? (n + 255) / 256 : 64),
+        // one thread per four elements where the sample's size allows 16-byte accesses
+        const bool vec = (n & 3) == 0 &&
+                         ((reinterpret_cast<uintptr_t>(a.workspace) | reinterpret_cast<uintptr_t>(a.gsf)) & 15u) == 0;
+        const long long work = vec ? n / 4 : n;
+        dim3 grid((unsigned)((work + 255) / 256 < 64 ? (work + 255) / 256 : 64),
                   (unsigned)(a.p.B < 32768 ? a.p.B : 32768));
         e = launch_overlapped(gsf_reduce_kernel<T>, grid, dim3(256), 0, stream, a.overlap_launch,
                               reinterpret_cast<const float*>(a.workspace), reinterpret_cast<T*>(a.gsf),
