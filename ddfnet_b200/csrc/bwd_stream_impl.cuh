@@ -409,10 +409,10 @@ bwd_filters_kernel(const __grid_constant__ BwdPlan pl) {
                     for (int t = 0; t < (DO_CF ? KK : 0); ++t) {
                         const uint32_t a = sfs + (uint32_t)(((t * pl.OH + oy) * pl.OW + ox0) * ES);
                         if constexpr (G::OUTB < 4) {
-                            sfr[t][0] = Word<T>::get(lds16(a), 0);
+                            sfr[t][0] = Word<T>::get(lds16v(a), 0);
                         } else {
                             uint32_t w[G::OUTB / 4];
-                            lds_vec<G::OUTB>(a, w);
+                            lds_vec<G::OUTB, true>(a, w);
                             if constexpr (PK) {
 #pragma unroll
                                 for (int q2 = 0; q2 < HP; ++q2)

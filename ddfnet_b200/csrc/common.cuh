@@ -127,6 +127,29 @@ __device__ __forceinline__ uint32_t lds32(uint32_t a) {
     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(a));
     return v;
 }
+// Volatile form: for values read from a buffer that is handed back (mbarrier arrive) right after
+// the read and kept in registers for a long time.  The assembler may otherwise move or repeat a
+// plain ld.shared closer to its first use, i.e. past the hand-back, where the buffer may already
+// hold the next data.
+__device__ __forceinline__ uint32_t lds32v(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.volatile.shared.b32 %0, [%1];" : "=r"(v) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16v(uint32_t a) {
+    uint16_t v;
+    asm volatile("ld.volatile.shared.u16 %0, [%1];" : "=h"(v) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ void lds64v(uint32_t a, uint32_t& x, uint32_t& y) {
+    asm volatile("ld.volatile.shared.v2.b32 {%0, %1}, [%2];" : "=r"(x), "=r"(y) : "r"(a) : "memory");
+}
+__device__ __forceinline__ void lds128v(uint32_t a, uint32_t& x, uint32_t& y, uint32_t& z, uint32_t& w) {
+    asm volatile("ld.volatile.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(x), "=r"(y), "=r"(z), "=r"(w)
+                 : "r"(a)
+                 : "memory");
+}
 __device__ __forceinline__ uint32_t lds16(uint32_t a) {
     uint16_t v;
     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));

@@ -479,9 +479,9 @@ ring_kernel(const __grid_constant__ RingPlan pl) {
 #pragma unroll
                         for (int r = 0; r < PH; ++r) {
                             const uint32_t a = sfs + (uint32_t)(((t * pl.OH + y0 + r) * pl.OW + x0) * 2);
-                            if constexpr (PW == 8) lds128(a, sfw[t][r * 4], sfw[t][r * 4 + 1], sfw[t][r * 4 + 2], sfw[t][r * 4 + 3]);
-                            else if constexpr (PW == 4) lds64(a, sfw[t][r * 2], sfw[t][r * 2 + 1]);
-                            else sfw[t][r] = lds32(a);
+                            if constexpr (PW == 8) lds128v(a, sfw[t][r * 4], sfw[t][r * 4 + 1], sfw[t][r * 4 + 2], sfw[t][r * 4 + 3]);
+                            else if constexpr (PW == 4) lds64v(a, sfw[t][r * 2], sfw[t][r * 2 + 1]);
+                            else sfw[t][r] = lds32v(a);
                         }
                     }
                 } else {
@@ -497,7 +497,7 @@ ring_kernel(const __grid_constant__ RingPlan pl) {
                                 const int yy = y0 + pp / PW + (i - G::R) * D, xx = x0 + pp % PW + (j - G::R) * D;
                                 uint32_t v = 0u;
                                 if (yy >= 0 && yy < pl.OH && xx >= 0 && xx < pl.OW)
-                                    v = lds16(sfs + (uint32_t)(((ft * pl.OH + yy) * pl.OW + xx) * 2));
+                                    v = lds16v(sfs + (uint32_t)(((ft * pl.OH + yy) * pl.OW + xx) * 2));
                                 if (pp & 1) sfw[i * K + j][pp / 2] |= v << 16;
                                 else sfw[i * K + j][pp / 2] = v;
                             }

@@ -1,29 +1,35 @@
-// Row kernel: DDF forward for planes whose output is 7 x 7 or 14 x 14 (the last two ddf_resnet
-// stages: 7 x 7 and 14 x 14 at stride 1, 14 x 14 -> 7 x 7 at stride 2), k = 3, dilation 1, 2-byte
-// element types.
+// Row kernel: DDF forward (and grad-x at stride 1) for square planes of the ddf_resnet stages,
+// k = 3, dilation 1, 2-byte element types: outputs 7, 14, 28 or 56 pixels wide at stride 1 and
+// 7, 14 or 28 wide at stride 2.
 //
-// Such planes are tiny (98 to 392 bytes) and there are tens of thousands of them; what a
-// launch costs is the time until the first arithmetic starts and the number of instructions
-// per output, not HBM time.  Hence:
+// The op costs 18 FMA-pipe operations per output, which at 2-byte I/O is as much time as the
+// HBM traffic; what decides a launch is the number of *other* instructions per output and the
+// time until the first arithmetic starts.  Hence:
 //
-//  * A thread owns one whole output row (OW = 7 or 14 pixels) of one plane per chunk of 448 / OW
-//    planes, and the same row position for the whole kernel: the 9 x OW spatial-filter values
-//    of its row stay in registers across all planes of a sample.  Because the row spans the
-//    full width, the left and right zero padding is known at compile time: those taps are
-//    simply not emitted (57 instead of 63 taps at OW = 7), and no halo masks exist.  Rows above
-//    and below the plane are redirected by one address select to a zeroed area.
-//  * Rows of 7 two-byte elements start on odd element offsets in every other row.  A row is
-//    read as four aligned words and brought into a fixed register layout by funnel shifts
+//  * A thread owns one output row, or a 14-pixel (stride 1) / 7-pixel (stride 2) segment of a
+//    row, at a fixed position for the whole kernel, and does one plane of every chunk of
+//    planes: the 9 x 14 (or 9 x 7) spatial-filter values of its pixels stay in registers,
+//    packed two to a word, across all planes of a sample.  With that many pixels per thread
+//    the window loads, the channel-filter loads, the stores and the loop cost about 10
+//    instructions per output next to the 18 FMAs (the 4-pixel patches of the plane-ring
+//    kernel: 20).
+//  * Whole rows (7 or 14 wide) know their left and right zero padding at compile time: those
+//    taps are simply not emitted (57 instead of 63 taps at 7 pixels), and no halo masks
+//    exist.  Segments AND the first word of a row's first window and the last word of its
+//    last window with per-thread constant masks.  Rows above and below the plane are
+//    redirected by one address select to a zeroed area.  Zero padding is exact in both modes.
+//  * Rows of 7 two-byte elements start on odd element offsets in every other row.  Such a row
+//    is read as four aligned words and brought into a fixed register layout by funnel shifts
 //    whose shift amount (0 or 16) is a per-thread constant; the arithmetic then selects
 //    fixed halves of fixed registers (mixed-precision FMA, see ring_fwd.cuh).  Rows of 14
-//    elements are word aligned and need no shifts.
-//  * The results of a row go to global memory as word stores (three words and one 2-byte
-//    store for 7 pixels); a warp's stores cover a contiguous run.
+//    or more elements are word aligned and need no shifts.  Outputs of 7 pixels leave as
+//    three word stores and one 2-byte store; a warp's stores cover a contiguous run.
 //  * Persistent CTA per SM; chunks of planes (plus their channel filters) arrive through a
 //    ring of shared-memory slots filled by untiled TMA bulk copies from one producer lane; a
 //    conversion warp turns each landed chunk's channel filters into the per-plane vector
-//    layout; 14 compute warps.  All of a CTA's chunks are usually in flight at once (a CTA's
-//    share is about 7 chunks), so the loads are limited by HBM, not by round trips.
+//    layout and announces them on a third mbarrier per slot; 14 compute warps of 32 threads
+//    (448 = 64 x 7 = 32 x 14 = 8 x 56 = 2 x 224 threads cover whole planes at every width).
+//    The spatial filters of two consecutive samples are double-buffered.
 //
 // Every mbarrier wait is bounded by the plan's wait_cycles (fault word + return, as in the
 // other streaming kernels).
@@ -278,14 +284,14 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                     const uint32_t a = sfs + (uint32_t)(t * OW * OW * 2);
                     if constexpr (OSHIFT) {
                         const uint32_t aw = a & ~3u, sh = (a & 2u) * 8u;
-                        const uint32_t w0 = lds32(aw), w1 = lds32(aw + 4), w2 = lds32(aw + 8), w3 = lds32(aw + 12);
+                        const uint32_t w0 = lds32v(aw), w1 = lds32v(aw + 4), w2 = lds32v(aw + 8), w3 = lds32v(aw + 12);
                         sfw[t][0] = __funnelshift_r(w0, w1, sh);
                         sfw[t][1] = __funnelshift_r(w1, w2, sh);
                         sfw[t][2] = __funnelshift_r(w2, w3, sh);
                         sfw[t][3] = w3 >> sh;
                     } else {
 #pragma unroll
-                        for (int q = 0; q < NSW; ++q) sfw[t][q] = lds32(a + 4u * q);
+                        for (int q = 0; q < NSW; ++q) sfw[t][q] = lds32v(a + 4u * q);
                     }
                 } else {
                     // window tap (ti, tj): filter plane KK-1-t, row y + ti - 1, elements
@@ -296,7 +302,7 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                     const uint32_t aw = a & ~3u, sh = (a & 2u) * 8u;
                     uint32_t wv[NSW + 1];
 #pragma unroll
-                    for (int q = 0; q <= NSW; ++q) wv[q] = lds32(aw + 4u * q);
+                    for (int q = 0; q <= NSW; ++q) wv[q] = lds32v(aw + 4u * q);
 #pragma unroll
                     for (int q = 0; q < NSW; ++q) sfw[t][q] = __funnelshift_r(wv[q], wv[q + 1], sh);
                     if (SEG % 2 != 0) sfw[t][NSW - 1] &= 0x0000ffffu;          // the half past the run

@@ -99,27 +99,36 @@ struct Geo {
     static_assert(ES == 2 || ES == 4, "2- and 4-byte element types only");
 };
 
-template <int NB>
+// VOL: volatile loads, for values that are kept in registers after their buffer has been
+// handed back (see lds32v in common.cuh).
+template <int NB, bool VOL = false>
 __device__ __forceinline__ void lds_vec(uint32_t a, uint32_t (&w)[NB / 4]) {
     if constexpr (NB == 4) {
-        w[0] = lds32(a);
+        w[0] = VOL ? lds32v(a) : lds32(a);
     } else if constexpr (NB == 8) {
-        lds64(a, w[0], w[1]);
+        if constexpr (VOL) lds64v(a, w[0], w[1]);
+        else lds64(a, w[0], w[1]);
     } else if constexpr (NB == 16) {
-        lds128(a, w[0], w[1], w[2], w[3]);
+        if constexpr (VOL) lds128v(a, w[0], w[1], w[2], w[3]);
+        else lds128(a, w[0], w[1], w[2], w[3]);
     } else {
         static_assert(NB == 32, "vector width");
-        lds128(a, w[0], w[1], w[2], w[3]);
-        lds128(a + 16, w[4], w[5], w[6], w[7]);
+        if constexpr (VOL) {
+            lds128v(a, w[0], w[1], w[2], w[3]);
+            lds128v(a + 16, w[4], w[5], w[6], w[7]);
+        } else {
+            lds128(a, w[0], w[1], w[2], w[3]);
+            lds128(a + 16, w[4], w[5], w[6], w[7]);
+        }
     }
 }
 
 // One input row of a thread's window, as floats.  rp = shared address of the
 // first main element (input column ox0*S of that row).
-template <typename T>
+template <typename T, bool VOL = false>
 __device__ __forceinline__ uint32_t lds_elem_bits(uint32_t a) {
-    if constexpr (sizeof(T) == 4) return lds32(a);
-    else return lds16(a);
+    if constexpr (sizeof(T) == 4) return VOL ? lds32v(a) : lds32(a);
+    else return VOL ? lds16v(a) : lds16(a);
 }
 
 template <typename T, typename G>
@@ -487,10 +496,10 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                         if constexpr (G::SUBWORD || G::OUTB < 4) {
 #pragma unroll
                             for (int pp = 0; pp < P; ++pp)
-                                set_sf(t, pp, Word<T>::get(lds_elem_bits<T>(a + pp * ES), 0));
+                                set_sf(t, pp, Word<T>::get(lds_elem_bits<T, true>(a + pp * ES), 0));
                         } else {
                             uint32_t w[G::OUTB / 4];
-                            lds_vec<G::OUTB>(a, w);
+                            lds_vec<G::OUTB, true>(a, w);
 #pragma unroll
                             for (int pp = 0; pp < P; ++pp)
                                 set_sf(t, pp, Word<T>::get(w[pp / G::EPW], pp % G::EPW));
@@ -558,8 +567,8 @@ stream_kernel(const __grid_constant__ StreamPlan pl) {
                                 float v = 0.f;
                                 if (yy >= 0 && yy < pl.OH && xx >= 0 && xx < pl.OW) {
                                     const uint32_t a = sfs + (uint32_t)(((ft * pl.OH + yy) * pl.OW + xx) * ES);
-                                    if constexpr (ES == 4) v = ldsf(a);
-                                    else v = Word<T>::get(lds16(a), 0);
+                                    if constexpr (ES == 4) v = __uint_as_float(lds32v(a));
+                                    else v = Word<T>::get(lds16v(a), 0);
                                 }
                                 set_sf(i * K + j, pp, v);
                             }

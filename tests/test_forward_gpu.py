@@ -99,6 +99,22 @@ def test_stream_forward(shape, dt):
     _no_fault()
 
 
+@pytest.mark.parametrize("shape", [(2100, 32, 14, 14, 3, 1, 1), (300, 8, 28, 28, 3, 1, 1), (400, 64, 7, 7, 3, 1, 1)])
+@pytest.mark.parametrize("mode", ["mul", "add"])
+def test_results_do_not_change_between_runs(shape, mode):
+    """A new sample every chunk makes the kernel recycle its two spatial-filter buffers as fast
+    as it can; a value read after its buffer was handed back shows up as a run-to-run
+    difference (the kernels have no atomics: equal inputs must give equal bits)."""
+    B, C, H, W, k, d, s = shape
+    dev = torch.device("cuda:0")
+    x, cf, sf = [t.to(dev) for t in make_inputs(B, C, H, W, k, s, torch.bfloat16, seed=5, with_go=False)]
+    from ddfnet_b200 import ddf
+    ref = ddf(x, cf, sf, k, d, s, mode, "f")
+    for _ in range(40):
+        assert torch.equal(ddf(x, cf, sf, k, d, s, mode, "f"), ref)
+    _no_fault()
+
+
 RAGGED = [(5, 32, 14, 14), (12, 32, 14, 14), (5, 64, 7, 7), (12, 64, 7, 7), (3, 24, 14, 14), (7, 8, 7, 7)]
 
 
