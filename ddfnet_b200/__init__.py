@@ -8,9 +8,10 @@ in include/ddf_b200.h.
 from .op import DDFFunction, DDFSpatialNormFunction, ddf, ddf_sfnorm
 from .modules import (DDFPack, DDFUpPack, FilterNorm, build_channel_branch,
                       build_spatial_branch)
+from ._lib import take_fault
 from .host import ddf_host, ddf_host_async
 from .layout import to_channels_last, to_nchw
 
 __all__ = ["ddf", "ddf_sfnorm", "DDFFunction", "DDFSpatialNormFunction", "DDFPack", "DDFUpPack", "FilterNorm",
            "build_spatial_branch", "build_channel_branch", "ddf_host", "ddf_host_async", "to_nchw",
-           "to_channels_last"]
+           "to_channels_last", "take_fault"]

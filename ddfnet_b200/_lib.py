@@ -116,6 +116,26 @@ class DDFError(RuntimeError):
         super().__init__(f"{msg.decode() if msg else 'ddf_b200 error'} (status {status})")
 
 
+# DDF_B200_DEBUG=1: after every call of the library, wait for the device and read the fault word
+# the TMA-fed kernels set when one of their bounded waits ran out (they then return early and
+# leave their output incomplete).  Costs a device synchronisation per call; skipped while a CUDA
+# graph is being captured.
+_DEBUG = os.environ.get("DDF_B200_DEBUG", "") == "1"
+
+
+def take_fault() -> int:
+    """Reads and clears the current device's fault word (synchronises the device).  0 = no
+    kernel gave up a wait since the last call; otherwise the code of the wait that ran out."""
+    return int(load().ddf_b200_take_fault())
+
+
 def check(status: int) -> None:
     if status != 0:
         raise DDFError(status)
+    if _DEBUG:
+        import torch
+        if torch.cuda.is_available() and not torch.cuda.is_current_stream_capturing():
+            fault = take_fault()
+            if fault != 0:
+                raise RuntimeError(f"ddf_b200: a kernel's bounded wait ran out (fault code {fault}); "
+                                   "the output of the last call is incomplete")

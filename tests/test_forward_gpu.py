@@ -143,7 +143,7 @@ def test_streaming_kernels_take_ragged_sizes(shape, dt):
     _no_fault()
 
 
-def test_wait_limit_reports_a_fault_and_the_context_survives():
+def test_wait_limit_reports_a_fault_and_the_context_survives(monkeypatch):
     """A bounded wait that runs out: every stage is announced 16 bytes larger than what is
     copied, so no stage ever completes; with a limit of about a millisecond the compute warps
     give up, the kernel returns, the fault word reads 1 (a compute warp gave up waiting for a
@@ -165,6 +165,12 @@ def test_wait_limit_reports_a_fault_and_the_context_survives():
     want = oracle_forward(x.cpu(), cf.cpu(), sf.cpu(), 3, 1, 1, "mul")
     check_close(out, want, torch.bfloat16, "after a starved launch")
     check_close(_run(x, cf, sf, 3, 1, 1, "mul"), want, torch.bfloat16, "ordinary call after a starved launch")
+    _no_fault()
+    # the Python mirror's debug mode (DDF_B200_DEBUG=1) turns a recorded fault into an exception
+    monkeypatch.setattr(lib, "_DEBUG", True)
+    with pytest.raises(RuntimeError, match="bounded wait ran out"):
+        lib.check(L.ddf_b200_forward_waitlimit(*args, 2_000_000, 1, stream))
+    monkeypatch.setattr(lib, "_DEBUG", False)
     _no_fault()
     # shapes outside the ring kernel's set are refused, not run
     xf = x.float()
