@@ -143,6 +143,12 @@ __global__ void __launch_bounds__(kNhwcThreads, 2) nhwc_forward_kernel(const Nhw
     };
     uint32_t sraw[PX][5];
     load_sf(sp, sraw);
+    // the spatial branch's bias (added before the FilterNorm), in registers for the whole strip
+    float bias[NORM ? KK : 1];
+    if constexpr (NORM) {
+#pragma unroll
+        for (int t = 0; t < KK; ++t) bias[t] = pl.sf_bias != nullptr ? __ldg(pl.sf_bias + t) : 0.f;
+    }
 
     uint32_t w0[NCOL][4], w1[NCOL][4], w2[NCOL][4];   // input rows oy*S - 1, oy*S, oy*S + 1
     load_row(oy0 * S - 1, w0);
@@ -169,7 +175,7 @@ __global__ void __launch_bounds__(kNhwcThreads, 2) nhwc_forward_kernel(const Nhw
                 float sum = 0.f;
 #pragma unroll
                 for (int t = 0; t < KK; ++t) {
-                    if (pl.sf_bias != nullptr) sfv[px][t] += __ldg(pl.sf_bias + t);
+                    sfv[px][t] += bias[t];
                     sum += sfv[px][t];
                 }
                 const float mean = sum * (1.f / KK);

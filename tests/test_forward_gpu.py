@@ -99,12 +99,14 @@ def test_stream_forward(shape, dt):
     _no_fault()
 
 
-@pytest.mark.parametrize("shape", [(2100, 32, 14, 14, 3, 1, 1), (300, 8, 28, 28, 3, 1, 1), (400, 64, 7, 7, 3, 1, 1)])
+@pytest.mark.parametrize("shape", [(2100, 32, 14, 14, 3, 1, 1), (300, 8, 28, 28, 3, 1, 1), (400, 64, 7, 7, 3, 1, 1),
+                                   (4800, 64, 7, 7, 3, 1, 1), (320, 16, 56, 56, 3, 1, 2), (96, 64, 56, 56, 3, 1, 1)])
 @pytest.mark.parametrize("mode", ["mul", "add"])
 def test_results_do_not_change_between_runs(shape, mode):
     """A new sample every chunk makes the kernel recycle its two spatial-filter buffers as fast
-    as it can; a value read after its buffer was handed back shows up as a run-to-run
-    difference (the kernels have no atomics: equal inputs must give equal bits)."""
+    as it can, and the last three shapes give every CTA several times more chunks than ring
+    slots; a value read after its buffer was handed back shows up as a run-to-run difference
+    (the kernels have no atomics: equal inputs must give equal bits)."""
     B, C, H, W, k, d, s = shape
     dev = torch.device("cuda:0")
     x, cf, sf = [t.to(dev) for t in make_inputs(B, C, H, W, k, s, torch.bfloat16, seed=5, with_go=False)]
