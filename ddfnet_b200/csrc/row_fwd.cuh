@@ -50,6 +50,7 @@ struct RowPlan {
     int chunks_per_sample;    // C / planes per chunk
     int n_slots;
     long long total_chunks;   // B * C / planes per chunk
+    int chunks_q, chunks_r;   // total_chunks = grid * q + r: CTA i takes q (+1 if i < r) chunks
     uint32_t chunk_bytes;     // one chunk of input planes
     uint32_t sf_bytes;        // 9 * OW * OW * 2
     unsigned long long sf_total, cf_total;
@@ -128,12 +129,14 @@ row_kernel(const __grid_constant__ RowPlan pl) {
     }
     if (tid < 4) sts128(sbase + pl.off_zero + 16u * (uint32_t)tid, 0u, 0u, 0u, 0u);
     __syncthreads();
+    // Programmatic dependent launch: this grid may have started while the previous one was still
+    // running.  Everything that does not touch global memory (index arithmetic, register set-up)
+    // comes before griddepcontrol.wait, which every role executes just before its main loop.
     asm volatile("griddepcontrol.launch_dependents;");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    const long long chunk_lo = (pl.total_chunks * (long long)blockIdx.x) / gridDim.x;
-    const long long chunk_hi = (pl.total_chunks * (long long)(blockIdx.x + 1)) / gridDim.x;
-    const int my_chunks = (int)(chunk_hi - chunk_lo);
+    const int bid = (int)blockIdx.x;
+    const long long chunk_lo = (long long)bid * pl.chunks_q + (bid < pl.chunks_r ? bid : pl.chunks_r);
+    const int my_chunks = pl.chunks_q + (bid < pl.chunks_r ? 1 : 0);
     if (my_chunks == 0) return;
     const int CPS = pl.chunks_per_sample;
 
@@ -142,10 +145,11 @@ row_kernel(const __grid_constant__ RowPlan pl) {
         if (lane != 0) return;
         bool ok = true;
         int seg = 0, issued = 0;
-        int b = (int)(chunk_lo / CPS);
+        int b = (int)chunk_lo / CPS;               // (the launcher keeps the chunk count below 2^31)
         int left_in_sample = 0;                    // chunks of sample b still to issue (0: start a sample)
         int first_left = CPS - (int)(chunk_lo - (long long)b * CPS);
         int slot = 0, round = 0;                   // chunk i uses slot i % NST in round i / NST
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int i = 0; i < my_chunks && ok; ++i) {
             const long long g = chunk_lo + i;
             if (left_in_sample == 0) {
@@ -192,6 +196,7 @@ row_kernel(const __grid_constant__ RowPlan pl) {
         // 2-byte values (add) every kRowCFP bytes
         int slot = 0;
         uint32_t ph = 0u;
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         for (int i = 0; i < my_chunks; ++i) {
             if (!mbar_wait_for(WBAR_FULL(slot), ph, pl.wait_cycles)) {
                 atomicCAS(pl.fault, 0, (int)kFaultConsumerFull);
@@ -257,9 +262,10 @@ row_kernel(const __grid_constant__ RowPlan pl) {
 
     int seg = 0, slot = 0;
     uint32_t ph = 0u;
-    int b = (int)(chunk_lo / CPS);
+    int b = (int)chunk_lo / CPS;
     int left_in_sample = 0;   // chunks of the current sample still to come (0: the next chunk starts a sample)
     const int first_left = CPS - (int)(chunk_lo - (long long)b * CPS);
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // (before the first store to global memory)
 #pragma unroll 1
     for (int i = 0; i < my_chunks; ++i) {
         if (!mbar_wait_for(WBAR_CF(slot), ph, pl.wait_cycles) ||
@@ -400,11 +406,18 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                         acc[p] = fmaf(yv[p], __uint_as_float(c[t]), acc[p]);
                     }
                 } else {
+                    // x * sf for every pixel, then x * cf (consecutive FMAs are independent and the
+                    // second group shares the channel-filter word)
 #pragma unroll
                     for (int p = 0; p < SEG; ++p) {
                         const int e = NSEG > 1 ? p * S + tj + 1 : p * S + tj - 1;
                         if (NSEG == 1 && (e < 0 || e >= W)) continue;
                         acc[p] = Mix<T>::fmaw(e & 1, p & 1, xw[ti][e >> 1], sfw[t][p >> 1], acc[p]);
+                    }
+#pragma unroll
+                    for (int p = 0; p < SEG; ++p) {
+                        const int e = NSEG > 1 ? p * S + tj + 1 : p * S + tj - 1;
+                        if (NSEG == 1 && (e < 0 || e >= W)) continue;
                         acc[p] = Mix<T>::fmaw(e & 1, t & 1, xw[ti][e >> 1], c[t >> 1], acc[p]);
                     }
                 }
@@ -461,6 +474,7 @@ int row_launch(const RowArgs& a, cudaStream_t stream) {
     pl.in = a.in; pl.cf = a.cf; pl.sf = a.sf; pl.out = a.out;
     pl.chunks_per_sample = p.C / kRowChunk;
     pl.total_chunks = (long long)p.B * pl.chunks_per_sample;
+    if (pl.total_chunks > 0x7fffffffll) return kNotHandled;
     pl.chunk_bytes = (uint32_t)(kRowChunk * W * W * 2);
     pl.sf_bytes = (uint32_t)(9 * OW * OW * 2);
     pl.sf_total = (unsigned long long)p.B * pl.sf_bytes;
@@ -485,6 +499,8 @@ int row_launch(const RowArgs& a, cudaStream_t stream) {
     pl.wait_cycles = kWaitCycles;
     const uint32_t smem = pl.off_stage0 + (uint32_t)slots * pl.stage_stride;
     const int grid = (int)(pl.total_chunks < a.sm_count ? pl.total_chunks : a.sm_count);
+    pl.chunks_q = (int)(pl.total_chunks / grid);
+    pl.chunks_r = (int)(pl.total_chunks % grid);
     auto kern = row_kernel<T, S, OW, NSEG, TPC, MODE, BWDX>;
     static std::atomic<unsigned long long> opted_in{0};
     const unsigned long long bit = 1ull << (a.device & 63);
