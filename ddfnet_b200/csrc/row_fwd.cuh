@@ -268,14 +268,10 @@ row_kernel(const __grid_constant__ RowPlan pl) {
     asm volatile("griddepcontrol.wait;" ::: "memory");   // (before the first store to global memory)
 #pragma unroll 1
     for (int i = 0; i < my_chunks; ++i) {
-        if (!mbar_wait_for(WBAR_CF(slot), ph, pl.wait_cycles) ||
-            !mbar_wait_for(WBAR_FULL(slot), ph, pl.wait_cycles)) {
-            atomicCAS(pl.fault, 0, (int)kFaultConsumerFull);
-            return;
-        }
         if (left_in_sample == 0) {
-            // a new sample: its spatial filter row (9 taps x OW pixels) into registers, as
-            // (p0,p1) (p2,p3) ... per tap
+            // a new sample: its spatial filter (requested before the chunk, hence taken first; at the
+            // start of a launch the registers fill while the first chunk is still in flight), 9 taps
+            // x SEG pixels as (p0,p1) (p2,p3) ... per tap
             const int buf = seg & 1;
             if (!mbar_wait_for(WBAR_SF_FULL(buf), (uint32_t)((seg >> 1) & 1), pl.wait_cycles)) {
                 atomicCAS(pl.fault, 0, (int)kFaultConsumerSf);
@@ -325,6 +321,12 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             if (lane == 0) mbar_arrive(WBAR_SF_EMPTY(buf));
             ++seg;
             left_in_sample = i == 0 ? first_left : CPS;
+        }
+        // the chunk has landed (full) and its channel filters are converted (cf)
+        if (!mbar_wait_for(WBAR_CF(slot), ph, pl.wait_cycles) ||
+            !mbar_wait_for(WBAR_FULL(slot), ph, pl.wait_cycles)) {
+            atomicCAS(pl.fault, 0, (int)kFaultConsumerFull);
+            return;
         }
         if (--left_in_sample == 0) ++b;
 
