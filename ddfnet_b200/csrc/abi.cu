@@ -248,6 +248,7 @@ static int run_row(const RowArgs& a, cudaStream_t st) {
     switch (a.p.dtype) {
         case DDF_B200_F16: rc = row_dispatch<__half>(a, st); break;
         case DDF_B200_BF16: rc = row_dispatch<__nv_bfloat16>(a, st); break;
+        case DDF_B200_F32: rc = row_dispatch<float>(a, st); break;
         default: rc = kNotHandled;
     }
     if (rc == 0) g_launches.fetch_add(1, std::memory_order_relaxed);

@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 SOURCES = ["abi.cu", "bwd_stream.cu", "layout.cu", "channel_branch.cu", "probe.cu", "nhwc.cu", "sfnorm.cu", "stream_inst_f32.cu", "stream_inst_f16.cu",
-           "stream_inst_bf16.cu", "ring_inst_f16.cu", "ring_inst_bf16.cu", "row_inst_f16.cu", "row_inst_bf16.cu", "bwd_inst_f32.cu", "bwd_inst_f16.cu", "bwd_inst_bf16.cu"]
+           "stream_inst_bf16.cu", "ring_inst_f16.cu", "ring_inst_bf16.cu", "row_inst_f16.cu", "row_inst_bf16.cu", "row_inst_f32.cu", "bwd_inst_f32.cu", "bwd_inst_f16.cu", "bwd_inst_bf16.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

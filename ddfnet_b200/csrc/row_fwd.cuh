@@ -1,6 +1,8 @@
 // Row kernel: DDF forward (and grad-x at stride 1) for square planes of the ddf_resnet stages,
-// k = 3, dilation 1, 2-byte element types: outputs 7, 14, 28 or 56 pixels wide at stride 1 and
-// 7, 14 or 28 wide at stride 2.
+// k = 3, dilation 1: outputs 7, 14, 28 or 56 pixels wide at stride 1 and, for the 2-byte element
+// types, 7, 14 or 28 wide at stride 2.  Written for the 2-byte types (the text below); float
+// elements run the same structure with one element per word, 7-pixel segments and plain float
+// multiply / FMA, where that measured faster than the plane-streaming kernel.
 //
 // The op costs 18 FMA-pipe operations per output, which at 2-byte I/O is as much time as the
 // HBM traffic; what decides a launch is the number of *other* instructions per output and the
@@ -55,6 +57,7 @@ struct RowPlan {
     uint32_t sf_bytes;        // 9 * OW * OW * 2
     unsigned long long sf_total, cf_total;
     uint32_t off_zero, off_sf, sf_stride, off_stage0, stage_stride, off_rawcf, off_conv;
+    int n_sfbuf;              // 1 or 2 buffers for the samples' spatial filters
     int* fault;
     long long wait_cycles;
 };
@@ -91,16 +94,22 @@ row_kernel(const __grid_constant__ RowPlan pl) {
     constexpr int CHT = kRowCompute / TPP;          // planes the compute threads cover at once
     constexpr int CH = CHT * TPC;                   // planes per chunk
     constexpr int W = OW * S;                       // input row length in elements
-    constexpr int PLANE = W * W * 2;                // input plane bytes
-    constexpr bool XSHIFT = W % 2 != 0;             // input rows start on odd elements: funnel shifts
-    constexpr bool OSHIFT = SEG % 2 != 0;           // the same for a thread's output and spatial-filter run
-    constexpr int NW = NSEG > 1 ? (S == 1 ? SEG / 2 + 2 : SEG + 1) : (W + 1) / 2;   // words of an input row a thread holds
-    constexpr int NSW = (SEG + 1) / 2;              // words of a thread's spatial-filter / output row
+    constexpr int ES = (int)sizeof(T);
+    constexpr bool F32 = ES == 4;                   // float: one element per word, plain FMUL / FFMA
+    constexpr int PLANE = W * W * ES;               // input plane bytes
+    constexpr bool XSHIFT = !F32 && W % 2 != 0;     // input rows start on odd elements: funnel shifts
+    constexpr bool OSHIFT = !F32 && SEG % 2 != 0;   // the same for a thread's output and spatial-filter run
+    // words of an input row a thread holds (2-byte: a segment's window starts two elements left
+    // of it, float: one element left)
+    constexpr int NW = F32 ? (NSEG > 1 ? SEG + 2 : W)
+                           : (NSEG > 1 ? (S == 1 ? SEG / 2 + 2 : SEG + 1) : (W + 1) / 2);
+    constexpr int NSW = F32 ? SEG : (SEG + 1) / 2;  // words of a thread's spatial-filter / output run
     static_assert(S == 1 || S == 2, "stride 1 or 2");
-    static_assert(NSEG == 1 ? (W == 7 || W == 14) : (S == 1 ? SEG == 14 : SEG == 7), "row or segment geometry");
+    static_assert(F32 ? (S == 1 && SEG == 7)
+                      : (NSEG == 1 ? (W == 7 || W == 14) : (S == 1 ? SEG == 14 : SEG == 7)), "row or segment geometry");
     static_assert(kRowCompute % TPP == 0, "whole planes per chunk");
     static_assert(!BWDX || S == 1, "grad-x at stride 1 only");
-    static_assert(sizeof(T) == 2, "2-byte element types only");
+    static_assert(ES == 2 || ES == 4, "2- and 4-byte element types");
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const uint32_t sbase = smem_u32(smem_raw);
@@ -154,8 +163,9 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             const long long g = chunk_lo + i;
             if (left_in_sample == 0) {
                 // this sample's spatial filter, into the buffer the sample before the previous one used
-                const int buf = seg & 1;
-                if (seg >= 2) ok = mbar_wait_for(WBAR_SF_EMPTY(buf), (uint32_t)(((seg >> 1) - 1) & 1), pl.wait_cycles);
+                const int buf = pl.n_sfbuf == 2 ? (seg & 1) : 0;
+                const int use = pl.n_sfbuf == 2 ? (seg >> 1) : seg;   // how often the buffer was used before
+                if (use >= 1) ok = mbar_wait_for(WBAR_SF_EMPTY(buf), (uint32_t)((use - 1) & 1), pl.wait_cycles);
                 if (!ok) break;
                 const unsigned long long g0 = (unsigned long long)b * pl.sf_bytes;
                 const Span sp = span_prepare(sbase + pl.off_sf + (uint32_t)buf * pl.sf_stride, pl.sf, g0,
@@ -170,7 +180,7 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             if (!ok) break;
             // the chunk's planes (a multiple of 16 bytes from a 16-byte aligned start) and their
             // channel filters (any byte range: aligned superset, clamped to the tensor's end)
-            constexpr unsigned long long cfb = (unsigned long long)(CH * KK * 2);
+            constexpr unsigned long long cfb = (unsigned long long)(CH * KK * ES);
             const Span sc = span_prepare(WSTAGE(slot) + pl.off_rawcf, pl.cf, (unsigned long long)g * cfb,
                                          (unsigned long long)(g + 1) * cfb, pl.cf_total);
             mbar_arrive_expect_tx(WBAR_FULL(slot), pl.chunk_bytes + sc.bytes);
@@ -185,8 +195,9 @@ row_kernel(const __grid_constant__ RowPlan pl) {
         bool landed = true;
         for (int j = (issued > NST ? issued - NST : 0); j < issued; ++j)
             landed &= mbar_wait_for(WBAR_FULL(j % NST), (uint32_t)((j / NST) & 1), pl.wait_cycles);
-        for (int s2 = (seg > 2 ? seg - 2 : 0); s2 < seg; ++s2)
-            landed &= mbar_wait_for(WBAR_SF_FULL(s2 & 1), (uint32_t)((s2 >> 1) & 1), pl.wait_cycles);
+        for (int s2 = (seg > pl.n_sfbuf ? seg - pl.n_sfbuf : 0); s2 < seg; ++s2)
+            landed &= mbar_wait_for(WBAR_SF_FULL(pl.n_sfbuf == 2 ? (s2 & 1) : 0),
+                                    (uint32_t)((pl.n_sfbuf == 2 ? (s2 >> 1) : s2) & 1), pl.wait_cycles);
         if (!landed) atomicCAS(pl.fault, 0, (int)kFaultDrain);
         return;
     }
@@ -203,15 +214,19 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                 return;
             }
             const uint32_t src = WSTAGE(slot) + pl.off_rawcf +
-                                 (uint32_t)(((unsigned long long)(chunk_lo + i) * (CH * KK * 2)) & 15ull);
+                                 (uint32_t)(((unsigned long long)(chunk_lo + i) * (CH * KK * ES)) & 15ull);
             const uint32_t dst = WSTAGE(slot) + pl.off_conv;
 #pragma unroll 3
             for (int e = lane; e < CH * KK; e += 32) {
                 const int u = e / KK, t = e - u * KK;
                 const int tt = BWDX ? KK - 1 - t : t;
-                const uint32_t raw = lds16(src + 2u * (uint32_t)e);
-                if constexpr (MODE == DDF_B200_MUL) sts32(dst + (uint32_t)(u * kRowCFP + 4 * tt), Mix<T>::f32_bits(raw));
-                else sts16(dst + (uint32_t)(u * kRowCFP + 2 * tt), raw);
+                if constexpr (F32) {
+                    sts32(dst + (uint32_t)(u * kRowCFP + 4 * tt), lds32(src + 4u * (uint32_t)e));
+                } else {
+                    const uint32_t raw = lds16(src + 2u * (uint32_t)e);
+                    if constexpr (MODE == DDF_B200_MUL) sts32(dst + (uint32_t)(u * kRowCFP + 4 * tt), Mix<T>::f32_bits(raw));
+                    else sts16(dst + (uint32_t)(u * kRowCFP + 2 * tt), raw);
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(WBAR_CF(slot));
@@ -233,7 +248,8 @@ row_kernel(const __grid_constant__ RowPlan pl) {
         const int iy = y * S - 1 + r;
         rowout[r] = iy < 0 || iy >= W;
         // (wraps for iy < 0: unused then)
-        const uint32_t a = 16u + (uint32_t)(j * PLANE + iy * W * 2 + (NSEG > 1 ? (g * SEG * S - 2) * 2 : 0));
+        // (a segment's window starts 4 bytes left of its first input element)
+        const uint32_t a = 16u + (uint32_t)(j * PLANE + iy * W * ES + (NSEG > 1 ? g * SEG * S * ES - 4 : 0));
         rowoff[r] = XSHIFT ? (a & ~3u) : a;
         rowsh[r] = XSHIFT ? (a & 2u) * 8u : 0u;
     }
@@ -251,8 +267,8 @@ row_kernel(const __grid_constant__ RowPlan pl) {
     const uint32_t opar = OSHIFT ? (uint32_t)((j * OW * OW + y * OW + g * SEG) & 1) : 0u;
     const uint32_t osh = opar * 16u;
     char* outp = reinterpret_cast<char*>(pl.out) +
-                 ((unsigned long long)chunk_lo * CH + (unsigned long long)j) * (OW * OW * 2) +
-                 (unsigned long long)((y * OW + g * SEG) * 2);
+                 ((unsigned long long)chunk_lo * CH + (unsigned long long)j) * (OW * OW * ES) +
+                 (unsigned long long)((y * OW + g * SEG) * ES);
 
     uint32_t sfw[KK][NSW];
 #pragma unroll
@@ -272,18 +288,18 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             // a new sample: its spatial filter (requested before the chunk, hence taken first; at the
             // start of a launch the registers fill while the first chunk is still in flight), 9 taps
             // x SEG pixels as (p0,p1) (p2,p3) ... per tap
-            const int buf = seg & 1;
-            if (!mbar_wait_for(WBAR_SF_FULL(buf), (uint32_t)((seg >> 1) & 1), pl.wait_cycles)) {
+            const int buf = pl.n_sfbuf == 2 ? (seg & 1) : 0;
+            if (!mbar_wait_for(WBAR_SF_FULL(buf), (uint32_t)((pl.n_sfbuf == 2 ? (seg >> 1) : seg) & 1), pl.wait_cycles)) {
                 atomicCAS(pl.fault, 0, (int)kFaultConsumerSf);
                 return;
             }
             const uint32_t sfs = sbase + pl.off_sf + (uint32_t)buf * pl.sf_stride +
                                  (uint32_t)(((unsigned long long)b * pl.sf_bytes) & 15ull) +
-                                 (uint32_t)((y * OW + g * SEG) * 2);
+                                 (uint32_t)((y * OW + g * SEG) * ES);
 #pragma unroll
             for (int t = 0; t < KK; ++t) {
                 if constexpr (!BWDX) {
-                    const uint32_t a = sfs + (uint32_t)(t * OW * OW * 2);
+                    const uint32_t a = sfs + (uint32_t)(t * OW * OW * ES);
                     if constexpr (OSHIFT) {
                         const uint32_t aw = a & ~3u, sh = (a & 2u) * 8u;
                         const uint32_t w0 = lds32v(aw), w1 = lds32v(aw + 4), w2 = lds32v(aw + 8), w3 = lds32v(aw + 12);
@@ -300,17 +316,24 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                     // g*SEG + tj - 1 + p (p = 0..SEG-1); what lies outside the plane is zero
                     const int ti = t / K, tj = t % K;
                     const int yy = y + ti - 1;
-                    const uint32_t a = sfs + (uint32_t)(((KK - 1 - t) * OW * OW + (ti - 1) * OW + (tj - 1)) * 2);
-                    const uint32_t aw = a & ~3u, sh = (a & 2u) * 8u;
-                    uint32_t wv[NSW + 1];
+                    const uint32_t a = sfs + (uint32_t)(((KK - 1 - t) * OW * OW + (ti - 1) * OW + (tj - 1)) * ES);
+                    if constexpr (F32) {
 #pragma unroll
-                    for (int q = 0; q <= NSW; ++q) wv[q] = lds32v(aw + 4u * q);
+                        for (int q = 0; q < NSW; ++q) sfw[t][q] = lds32v(a + 4u * q);
+                        if (tj == 0 && g == 0) sfw[t][0] = 0u;                     // column -1
+                        if (tj == 2 && g == NSEG - 1) sfw[t][NSW - 1] = 0u;        // column OW
+                    } else {
+                        const uint32_t aw = a & ~3u, sh = (a & 2u) * 8u;
+                        uint32_t wv[NSW + 1];
 #pragma unroll
-                    for (int q = 0; q < NSW; ++q) sfw[t][q] = __funnelshift_r(wv[q], wv[q + 1], sh);
-                    if (SEG % 2 != 0) sfw[t][NSW - 1] &= 0x0000ffffu;          // the half past the run
-                    if (tj == 0 && g == 0) sfw[t][0] &= 0xffff0000u;           // column -1
-                    if (tj == 2 && g == NSEG - 1)                              // column OW
-                        sfw[t][NSW - 1] &= (SEG % 2 != 0) ? 0u : 0x0000ffffu;
+                        for (int q = 0; q <= NSW; ++q) wv[q] = lds32v(aw + 4u * q);
+#pragma unroll
+                        for (int q = 0; q < NSW; ++q) sfw[t][q] = __funnelshift_r(wv[q], wv[q + 1], sh);
+                        if (SEG % 2 != 0) sfw[t][NSW - 1] &= 0x0000ffffu;          // the half past the run
+                        if (tj == 0 && g == 0) sfw[t][0] &= 0xffff0000u;           // column -1
+                        if (tj == 2 && g == NSEG - 1)                              // column OW
+                            sfw[t][NSW - 1] &= (SEG % 2 != 0) ? 0u : 0x0000ffffu;
+                    }
                     if (yy < 0 || yy >= OW) {
 #pragma unroll
                         for (int q = 0; q < NSW; ++q) sfw[t][q] = 0u;
@@ -335,7 +358,7 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             // task u of the chunk: plane u * CHT + j
             const uint32_t st = WSTAGE(slot) + (uint32_t)(u * CHT * PLANE);
             const uint32_t ca0 = WSTAGE(slot) + cfoff + (uint32_t)(u * CHT * kRowCFP);
-            char* op = outp + u * (CHT * OW * OW * 2);
+            char* op = outp + u * (CHT * OW * OW * ES);
             // ---- the plane's input rows
             uint32_t xw[K][NW];
 #pragma unroll
@@ -374,7 +397,7 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             uint32_t c[12];
             {
                 const uint32_t ca = ca0;
-                if constexpr (MODE == DDF_B200_MUL) {
+                if constexpr (MODE == DDF_B200_MUL || F32) {
                     lds128(ca, c[0], c[1], c[2], c[3]);
                     lds128(ca + 16, c[4], c[5], c[6], c[7]);
                     c[8] = lds32(ca + 32);
@@ -395,6 +418,33 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                 // Pixels are taken HB at a time: whole rows (NSEG = 1) measured faster seven at a time
                 // (14 x 14, mul: 13.0 -> 9.8 us), segments all fourteen at once (56 x 56, mul: 34.7 against 37.4 us).
                 constexpr int HB = (NSEG == 1 && SEG > 7) ? 7 : SEG;
+                if constexpr (F32) {
+                    // float: window element p + tj (a segment's window starts one element left of it).
+                    // mul: the filter product sf * cf first (it does not wait for the window loads),
+                    // then one FMA per pixel; add: two FMAs per pixel.
+                    const float cv = __uint_as_float(c[t]);
+                    float wv[SEG];
+                    if constexpr (MODE == DDF_B200_MUL) {
+#pragma unroll
+                        for (int p = 0; p < SEG; ++p) wv[p] = __uint_as_float(sfw[t][p]) * cv;
+                    }
+#pragma unroll
+                    for (int p = 0; p < SEG; ++p) {
+                        const int e = NSEG > 1 ? p + tj : p + tj - 1;
+                        if (NSEG == 1 && (e < 0 || e >= W)) continue;
+                        const float xv = __uint_as_float(xw[ti][e]);
+                        if constexpr (MODE == DDF_B200_MUL) acc[p] = fmaf(xv, wv[p], acc[p]);
+                        else acc[p] = fmaf(xv, __uint_as_float(sfw[t][p]), acc[p]);
+                    }
+                    if constexpr (MODE == DDF_B200_ADD) {
+#pragma unroll
+                        for (int p = 0; p < SEG; ++p) {
+                            const int e = NSEG > 1 ? p + tj : p + tj - 1;
+                            if (NSEG == 1 && (e < 0 || e >= W)) continue;
+                            acc[p] = fmaf(__uint_as_float(xw[ti][e]), cv, acc[p]);
+                        }
+                    }
+                } else
 #pragma unroll
                 for (int p0 = 0; p0 < SEG; p0 += HB) {
                     if constexpr (MODE == DDF_B200_MUL) {
@@ -435,7 +485,10 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                 }
             }
             // ---- store the row
-            if constexpr (OSHIFT) {
+            if constexpr (F32) {
+#pragma unroll
+                for (int q = 0; q < SEG; ++q) stg32(op + 4 * q, __float_as_uint(acc[q]));
+            } else if constexpr (OSHIFT) {
                 // 7 results: three words and one half, arranged by the row's word parity
                 const uint32_t w0 = Word<T>::put(acc[0], acc[1]), w1 = Word<T>::put(acc[2], acc[3]);
                 const uint32_t w2 = Word<T>::put(acc[4], acc[5]), w3 = Word<T>::put(acc[6], 0.f);
@@ -451,7 +504,7 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                 for (int q = 0; q < NSW; ++q) stg32(op + 4 * q, Word<T>::put(acc[2 * q], acc[2 * q + 1]));
             }
         }
-        outp += CH * OW * OW * 2;
+        outp += CH * OW * OW * ES;
         __syncwarp();
         if (lane == 0) mbar_arrive(WBAR_EMPTY(slot));
         if (++slot == NST) { slot = 0; ph ^= 1u; }
@@ -481,26 +534,35 @@ template <typename T, int S, int OW, int NSEG, int TPC, int MODE, bool BWDX>
 int row_launch(const RowArgs& a, cudaStream_t stream) {
     const Problem& p = a.p;
     constexpr int W = OW * S;
+    constexpr int ES = (int)sizeof(T);
     constexpr int kRowChunk = TPC * (kRowCompute / (OW * NSEG));
     RowPlan pl;
     pl.in = a.in; pl.cf = a.cf; pl.sf = a.sf; pl.out = a.out;
     pl.chunks_per_sample = p.C / kRowChunk;
     pl.total_chunks = (long long)p.B * pl.chunks_per_sample;
     if (pl.total_chunks > 0x7fffffffll) return kNotHandled;
-    pl.chunk_bytes = (uint32_t)(kRowChunk * W * W * 2);
-    pl.sf_bytes = (uint32_t)(9 * OW * OW * 2);
+    pl.chunk_bytes = (uint32_t)(kRowChunk * W * W * ES);
+    pl.sf_bytes = (uint32_t)(9 * OW * OW * ES);
     pl.sf_total = (unsigned long long)p.B * pl.sf_bytes;
-    pl.cf_total = (unsigned long long)p.B * p.C * 18ull;
+    pl.cf_total = (unsigned long long)p.B * p.C * (9ull * ES);
     pl.off_zero = round_up(8u * (3 * kRowMaxSlots + 4), 16);
     pl.off_sf = round_up(pl.off_zero + 64u, 128);
     pl.sf_stride = round_up(pl.sf_bytes + 48u, 128);
+    // two spatial-filter buffers (the next sample's filter arrives while this one is in use) unless
+    // that would leave fewer than three ring slots; then one
+    pl.n_sfbuf = 2;
     pl.off_stage0 = pl.off_sf + 2u * pl.sf_stride;
     // [16 bytes: a first segment's window starts 4 bytes early][planes][16 bytes: a last row's or
     // last segment's window runs up to 14 bytes over][raw channel filters + alignment slack]
     pl.off_rawcf = round_up(16u + pl.chunk_bytes + 16u, 16);
-    pl.off_conv = round_up(pl.off_rawcf + (uint32_t)(kRowChunk * 9 * 2) + 32u, 16);
+    pl.off_conv = round_up(pl.off_rawcf + (uint32_t)(kRowChunk * 9 * ES) + 32u, 16);
     pl.stage_stride = round_up(pl.off_conv + (uint32_t)(kRowChunk * kRowCFP), 128);
     const long long share = (pl.total_chunks + a.sm_count - 1) / a.sm_count;
+    if (pl.off_stage0 + 3u * pl.stage_stride > kSmemBudget) {
+        pl.n_sfbuf = 1;
+        pl.off_stage0 = pl.off_sf + pl.sf_stride;
+    }
+    if (pl.off_stage0 + pl.stage_stride > kSmemBudget) return kNotHandled;
     int slots = (int)((kSmemBudget - pl.off_stage0) / pl.stage_stride);
     if (slots > kRowMaxSlots) slots = kRowMaxSlots;
     if (slots > share) slots = (int)share;
@@ -529,12 +591,20 @@ int row_launch(const RowArgs& a, cudaStream_t stream) {
 // problem is not covered.
 inline int row_planes_at_once(const RowArgs& a) {
     const Problem& p = a.p;
-    if (p.dtype != DDF_B200_F16 && p.dtype != DDF_B200_BF16) return 0;
+    if (p.dtype != DDF_B200_F16 && p.dtype != DDF_B200_BF16 && p.dtype != DDF_B200_F32) return 0;
     if (p.k != 3 || p.d != 1 || (p.s != 1 && p.s != 2) || p.sf_norm) return 0;
     if (a.bwdx && p.s != 1) return 0;
     if (p.OH != p.OW || p.H != p.OH * p.s || p.W != p.OW * p.s) return 0;
     int tpp;   // threads per plane
-    if (p.OW == 7) tpp = 7;
+    if (p.dtype == DDF_B200_F32) {
+        // float: 7-pixel segments, stride 1
+        if (p.s != 1 || (p.OW != 7 && p.OW != 14 && p.OW != 28 && p.OW != 56)) return 0;
+        // measured against the plane-streaming kernel (B = 128, us): add 57.0 / 26.9 / 18.1 / 10.3
+        // against 60.6 / 28.1 / 20.8 / 13.3 at 56 / 28 / 14 / 7 pixels; mul 62.1 / 30.7 / 18.3 / 11.0
+        // against the same: mul stays with the streaming kernel at the two large widths
+        if (p.combine == DDF_B200_MUL && p.OW >= 28) return 0;
+        tpp = p.OW * (p.OW / 7);
+    } else if (p.OW == 7) tpp = 7;
     else if (p.s == 1 && (p.OW == 14 || p.OW == 28 || p.OW == 56)) tpp = p.OW * (p.OW / 14);
     else if (p.s == 2 && (p.OW == 14 || p.OW == 28)) tpp = p.OW * (p.OW / 7);
     else return 0;
