@@ -57,7 +57,6 @@ struct RowPlan {
     uint32_t sf_bytes;        // 9 * OW * OW * 2
     unsigned long long sf_total, cf_total;
     uint32_t off_zero, off_sf, sf_stride, off_stage0, stage_stride, off_rawcf, off_conv;
-    int n_sfbuf;              // 1 or 2 buffers for the samples' spatial filters
     int* fault;
     long long wait_cycles;
 };
@@ -104,6 +103,9 @@ row_kernel(const __grid_constant__ RowPlan pl) {
     constexpr int NW = F32 ? (NSEG > 1 ? SEG + 2 : W)
                            : (NSEG > 1 ? (S == 1 ? SEG / 2 + 2 : SEG + 1) : (W + 1) / 2);
     constexpr int NSW = F32 ? SEG : (SEG + 1) / 2;  // words of a thread's spatial-filter / output run
+    // buffers for the samples' spatial filters: two (the next sample's filter arrives while this one is
+    // in use), except for 56 x 56 float planes, where one sample's filter is 113 KB
+    constexpr int NSFB = (F32 && OW == 56) ? 1 : 2;
     static_assert(S == 1 || S == 2, "stride 1 or 2");
     static_assert(F32 ? (S == 1 && SEG == 7)
                       : (NSEG == 1 ? (W == 7 || W == 14) : (S == 1 ? SEG == 14 : SEG == 7)), "row or segment geometry");
@@ -163,8 +165,8 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             const long long g = chunk_lo + i;
             if (left_in_sample == 0) {
                 // this sample's spatial filter, into the buffer the sample before the previous one used
-                const int buf = pl.n_sfbuf == 2 ? (seg & 1) : 0;
-                const int use = pl.n_sfbuf == 2 ? (seg >> 1) : seg;   // how often the buffer was used before
+                const int buf = NSFB == 2 ? (seg & 1) : 0;
+                const int use = NSFB == 2 ? (seg >> 1) : seg;   // how often the buffer was used before
                 if (use >= 1) ok = mbar_wait_for(WBAR_SF_EMPTY(buf), (uint32_t)((use - 1) & 1), pl.wait_cycles);
                 if (!ok) break;
                 const unsigned long long g0 = (unsigned long long)b * pl.sf_bytes;
@@ -195,9 +197,9 @@ row_kernel(const __grid_constant__ RowPlan pl) {
         bool landed = true;
         for (int j = (issued > NST ? issued - NST : 0); j < issued; ++j)
             landed &= mbar_wait_for(WBAR_FULL(j % NST), (uint32_t)((j / NST) & 1), pl.wait_cycles);
-        for (int s2 = (seg > pl.n_sfbuf ? seg - pl.n_sfbuf : 0); s2 < seg; ++s2)
-            landed &= mbar_wait_for(WBAR_SF_FULL(pl.n_sfbuf == 2 ? (s2 & 1) : 0),
-                                    (uint32_t)((pl.n_sfbuf == 2 ? (s2 >> 1) : s2) & 1), pl.wait_cycles);
+        for (int s2 = (seg > NSFB ? seg - NSFB : 0); s2 < seg; ++s2)
+            landed &= mbar_wait_for(WBAR_SF_FULL(NSFB == 2 ? (s2 & 1) : 0),
+                                    (uint32_t)((NSFB == 2 ? (s2 >> 1) : s2) & 1), pl.wait_cycles);
         if (!landed) atomicCAS(pl.fault, 0, (int)kFaultDrain);
         return;
     }
@@ -288,8 +290,8 @@ row_kernel(const __grid_constant__ RowPlan pl) {
             // a new sample: its spatial filter (requested before the chunk, hence taken first; at the
             // start of a launch the registers fill while the first chunk is still in flight), 9 taps
             // x SEG pixels as (p0,p1) (p2,p3) ... per tap
-            const int buf = pl.n_sfbuf == 2 ? (seg & 1) : 0;
-            if (!mbar_wait_for(WBAR_SF_FULL(buf), (uint32_t)((pl.n_sfbuf == 2 ? (seg >> 1) : seg) & 1), pl.wait_cycles)) {
+            const int buf = NSFB == 2 ? (seg & 1) : 0;
+            if (!mbar_wait_for(WBAR_SF_FULL(buf), (uint32_t)((NSFB == 2 ? (seg >> 1) : seg) & 1), pl.wait_cycles)) {
                 atomicCAS(pl.fault, 0, (int)kFaultConsumerSf);
                 return;
             }
@@ -548,20 +550,15 @@ int row_launch(const RowArgs& a, cudaStream_t stream) {
     pl.off_zero = round_up(8u * (3 * kRowMaxSlots + 4), 16);
     pl.off_sf = round_up(pl.off_zero + 64u, 128);
     pl.sf_stride = round_up(pl.sf_bytes + 48u, 128);
-    // two spatial-filter buffers (the next sample's filter arrives while this one is in use) unless
-    // that would leave fewer than three ring slots; then one
-    pl.n_sfbuf = 2;
-    pl.off_stage0 = pl.off_sf + 2u * pl.sf_stride;
+    // spatial-filter buffers: as the kernel's NSFB
+    constexpr uint32_t kSfBufs = (ES == 4 && OW == 56) ? 1u : 2u;
+    pl.off_stage0 = pl.off_sf + kSfBufs * pl.sf_stride;
     // [16 bytes: a first segment's window starts 4 bytes early][planes][16 bytes: a last row's or
     // last segment's window runs up to 14 bytes over][raw channel filters + alignment slack]
     pl.off_rawcf = round_up(16u + pl.chunk_bytes + 16u, 16);
     pl.off_conv = round_up(pl.off_rawcf + (uint32_t)(kRowChunk * 9 * ES) + 32u, 16);
     pl.stage_stride = round_up(pl.off_conv + (uint32_t)(kRowChunk * kRowCFP), 128);
     const long long share = (pl.total_chunks + a.sm_count - 1) / a.sm_count;
-    if (pl.off_stage0 + 3u * pl.stage_stride > kSmemBudget) {
-        pl.n_sfbuf = 1;
-        pl.off_stage0 = pl.off_sf + pl.sf_stride;
-    }
     if (pl.off_stage0 + pl.stage_stride > kSmemBudget) return kNotHandled;
     int slots = (int)((kSmemBudget - pl.off_stage0) / pl.stage_stride);
     if (slots > kRowMaxSlots) slots = kRowMaxSlots;
