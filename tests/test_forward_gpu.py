@@ -117,6 +117,26 @@ def test_results_do_not_change_between_runs(shape, mode):
     _no_fault()
 
 
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("mode", ["mul", "add"])
+def test_gradients_do_not_change_between_runs(dt, mode):
+    """The same for the backward: grad-x runs in the row kernel with the spatial-filter registers
+    gathered from a recycled buffer, and the two filter gradients are summed in a fixed order."""
+    from ddfnet_b200 import ddf
+    dev = torch.device("cuda:0")
+    B, C, H = 300, 8, 28
+    x, cf, sf, go = [t.to(dev) for t in make_inputs(B, C, H, H, 3, 1, DTYPES[dt], seed=6)]
+    def grads():
+        xs = [t.detach().requires_grad_() for t in (x, cf, sf)]
+        ddf(*xs, 3, 1, 1, mode).backward(go)
+        return [t.grad for t in xs]
+    ref = grads()
+    for _ in range(20):
+        for a, b in zip(grads(), ref):
+            assert torch.equal(a, b)
+    _no_fault()
+
+
 RAGGED = [(5, 32, 14, 14), (12, 32, 14, 14), (5, 64, 7, 7), (12, 64, 7, 7), (3, 24, 14, 14), (7, 8, 7, 7)]
 
 
