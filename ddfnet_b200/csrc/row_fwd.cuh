@@ -422,28 +422,39 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                 constexpr int HB = (NSEG == 1 && SEG > 7) ? 7 : SEG;
                 if constexpr (F32) {
                     // float: window element p + tj (a segment's window starts one element left of it).
-                    // mul: the filter product sf * cf first (it does not wait for the window loads),
-                    // then one FMA per pixel; add: two FMAs per pixel.
+                    // mul: the filter product sf * cf first, then one FMA per pixel; add: two FMAs per pixel.
+                    // Pixels in pairs through the packed f32x2 instructions (one issue slot for two
+                    // FMAs), a last odd pixel and pairs with a dropped tap in scalar form.
                     const float cv = __uint_as_float(c[t]);
-                    float wv[SEG];
-                    if constexpr (MODE == DDF_B200_MUL) {
+                    const unsigned long long cc = f2_pack(cv, cv);
 #pragma unroll
-                        for (int p = 0; p < SEG; ++p) wv[p] = __uint_as_float(sfw[t][p]) * cv;
-                    }
-#pragma unroll
-                    for (int p = 0; p < SEG; ++p) {
-                        const int e = NSEG > 1 ? p + tj : p + tj - 1;
-                        if (NSEG == 1 && (e < 0 || e >= W)) continue;
-                        const float xv = __uint_as_float(xw[ti][e]);
-                        if constexpr (MODE == DDF_B200_MUL) acc[p] = fmaf(xv, wv[p], acc[p]);
-                        else acc[p] = fmaf(xv, __uint_as_float(sfw[t][p]), acc[p]);
-                    }
-                    if constexpr (MODE == DDF_B200_ADD) {
-#pragma unroll
-                        for (int p = 0; p < SEG; ++p) {
-                            const int e = NSEG > 1 ? p + tj : p + tj - 1;
-                            if (NSEG == 1 && (e < 0 || e >= W)) continue;
-                            acc[p] = fmaf(__uint_as_float(xw[ti][e]), cv, acc[p]);
+                    for (int p = 0; p < SEG; p += 2) {
+                        const int e0 = NSEG > 1 ? p + tj : p + tj - 1;
+                        const int e1 = e0 + 1;
+                        const bool v0 = NSEG > 1 || (e0 >= 0 && e0 < W);
+                        const bool v1 = p + 1 < SEG && (NSEG > 1 || (e1 >= 0 && e1 < W));
+                        if (v0 && v1) {
+                            const unsigned long long xp = f2_pack(__uint_as_float(xw[ti][e0]), __uint_as_float(xw[ti][e1]));
+                            const unsigned long long sp = f2_pack(__uint_as_float(sfw[t][p]), __uint_as_float(sfw[t][p + 1]));
+                            unsigned long long ap = f2_pack(acc[p], acc[p + 1]);
+                            if constexpr (MODE == DDF_B200_MUL) {
+                                ap = f2_fma(xp, f2_mul(sp, cc), ap);
+                            } else {
+                                ap = f2_fma(xp, sp, ap);
+                                ap = f2_fma(xp, cc, ap);
+                            }
+                            f2_unpack(ap, acc[p], acc[p + 1]);
+                        } else {
+                            if (v0) {
+                                const float xv = __uint_as_float(xw[ti][e0]), sv = __uint_as_float(sfw[t][p]);
+                                if constexpr (MODE == DDF_B200_MUL) acc[p] = fmaf(xv, sv * cv, acc[p]);
+                                else acc[p] = fmaf(xv, cv, fmaf(xv, sv, acc[p]));
+                            }
+                            if (v1) {
+                                const float xv = __uint_as_float(xw[ti][e1]), sv = __uint_as_float(sfw[t][p + 1]);
+                                if constexpr (MODE == DDF_B200_MUL) acc[p + 1] = fmaf(xv, sv * cv, acc[p + 1]);
+                                else acc[p + 1] = fmaf(xv, cv, fmaf(xv, sv, acc[p + 1]));
+                            }
                         }
                     }
                 } else
@@ -459,12 +470,24 @@ row_kernel(const __grid_constant__ RowPlan pl) {
                             if (NSEG == 1 && (e < 0 || e >= W)) continue;
                             yv[q] = Mix<T>::fmaw(e & 1, p & 1, xw[ti][e >> 1], sfw[t][p >> 1], 0.f);
                         }
+                        // two pixels per instruction where both take part (fma.rn.f32x2 is the same
+                        // IEEE fma per lane and half the issue slots: 56 x 56, 34.9 -> 28.9 us)
+                        const unsigned long long cc = f2_pack(__uint_as_float(c[t]), __uint_as_float(c[t]));
 #pragma unroll
-                        for (int q = 0; q < HB; ++q) {
+                        for (int q = 0; q < HB; q += 2) {
                             const int p = p0 + q;
-                            const int e = NSEG > 1 ? p * S + tj + 1 : p * S + tj - 1;
-                            if (NSEG == 1 && (e < 0 || e >= W)) continue;
-                            acc[p] = fmaf(yv[q], __uint_as_float(c[t]), acc[p]);
+                            const int e0 = NSEG > 1 ? p * S + tj + 1 : p * S + tj - 1;
+                            const int e1 = e0 + S;
+                            const bool v0 = NSEG > 1 || (e0 >= 0 && e0 < W);
+                            const bool v1 = q + 1 < HB && (NSEG > 1 || (e1 >= 0 && e1 < W));
+                            if (v0 && v1) {
+                                const unsigned long long r =
+                                    f2_fma(f2_pack(yv[q], yv[q + 1]), cc, f2_pack(acc[p], acc[p + 1]));
+                                f2_unpack(r, acc[p], acc[p + 1]);
+                            } else {
+                                if (v0) acc[p] = fmaf(yv[q], __uint_as_float(c[t]), acc[p]);
+                                if (v1) acc[p + 1] = fmaf(yv[q + 1], __uint_as_float(c[t]), acc[p + 1]);
+                            }
                         }
                     } else {
                         // x * sf for every pixel, then x * cf (consecutive FMAs are independent and the
@@ -596,10 +619,8 @@ inline int row_planes_at_once(const RowArgs& a) {
     if (p.dtype == DDF_B200_F32) {
         // float: 7-pixel segments, stride 1
         if (p.s != 1 || (p.OW != 7 && p.OW != 14 && p.OW != 28 && p.OW != 56)) return 0;
-        // measured against the plane-streaming kernel (B = 128, us): add 57.0 / 26.9 / 18.1 / 10.3
-        // against 60.6 / 28.1 / 20.8 / 13.3 at 56 / 28 / 14 / 7 pixels; mul 62.1 / 30.7 / 18.3 / 11.0
-        // against the same: mul stays with the streaming kernel at the two large widths
-        if (p.combine == DDF_B200_MUL && p.OW >= 28) return 0;
+        // (measured against the plane-streaming kernel, B = 128, us at 56 / 28 / 14 / 7 pixels:
+        // mul 41.8 / 21.1 / 15.5 / 10.6 and add 48.3 / 23.9 / 14.0 / 10.3 against 60.6 / 28.1 / 20.8 / 13.3)
         tpp = p.OW * (p.OW / 7);
     } else if (p.OW == 7) tpp = 7;
     else if (p.s == 1 && (p.OW == 14 || p.OW == 28 || p.OW == 56)) tpp = p.OW * (p.OW / 14);
