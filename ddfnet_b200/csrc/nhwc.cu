@@ -215,12 +215,17 @@ __global__ void __launch_bounds__(kNhwcThreads, 2) nhwc_forward_kernel(const Nhw
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const uint32_t xw = i == 0 ? w0[cidx][q] : (i == 1 ? w1[cidx][q] : w2[cidx][q]);
+                        if constexpr (MODE == DDF_B200_MUL) {
+                            // the two channels of a word: exact products, then one packed f32x2 FMA
+                            // against the tap's spatial-filter value (half the issue slots of two FFMAs)
+                            const float y0 = Mix<T>::fmaw(0, 0, xw, cfw[t][q], 0.f);
+                            const float y1 = Mix<T>::fmaw(1, 1, xw, cfw[t][q], 0.f);
+                            const unsigned long long r = f2_fma(f2_pack(y0, y1), f2_pack(sfv[px][t], sfv[px][t]),
+                                                                f2_pack(acc[px][2 * q], acc[px][2 * q + 1]));
+                            f2_unpack(r, acc[px][2 * q], acc[px][2 * q + 1]);
+                        } else {
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            if constexpr (MODE == DDF_B200_MUL) {
-                                const float y = Mix<T>::fmaw(h, h, xw, cfw[t][q], 0.f);
-                                acc[px][2 * q + h] = fmaf(y, sfv[px][t], acc[px][2 * q + h]);
-                            } else {
+                            for (int h = 0; h < 2; ++h) {
                                 float a = acc[px][2 * q + h];
                                 a = Mix<T>::fmaw(h, h, xw, cfw[t][q], a);
                                 a = Mix<T>::fmaw(h, t & 1, xw, sfh[px][t / 2], a);
