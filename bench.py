@@ -267,6 +267,10 @@ def run_ours(args, rank, world, local_rank):
         # per-call durations: each call replayed alone from its own graph over rotating
         # buffer sets larger than L2, timed with CUDA events
         floor_us = launch_floor_us(L)
+        # issue rate of the mixed-precision FMA (warp instructions per ns per SM), measured live by the
+        # library's probe kernel: the second roof of the 2-byte stride-1 shapes (18 FMA operations per output)
+        fma_rate = mixed_fma_rate(L, dev) if rank == 0 and not args.quick else None
+        sm_count = torch.cuda.get_device_properties(dev).multi_processor_count
         per_shape = []
         if rank == 0 and not args.quick:
             for (mode, dtname, C, H, s, x, cf, sf) in cases:
@@ -395,6 +399,14 @@ def run_ours(args, rank, world, local_rank):
                 "achieved": dom["gbs"], "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
                 "frac": round(dom["gbs"] / peak, 4), "frac_of_8000": round(dom["gbs"] / 8000.0, 4),
                 "traffic": None, "us_per_launch": dom["us"], "algorithmic_bytes": dom["bytes"]}
+        if fma_rate:
+            # the same launch against the FMA-issue roof: k*k taps x 2 FMA operations per output
+            oh = dom["H"] // dom["stride"]
+            ops = BATCH * dom["C"] * oh * oh * 2 * K * K
+            fma_us = ops / 32 / (sm_count * fma_rate) / 1e3
+            roof["fma_issue_roof"] = {"rate_warp_instr_per_ns_per_sm": fma_rate, "floor_us": round(fma_us, 2),
+                                      "hbm_floor_us": round(dom["bytes"] / peak / 1e3, 2),
+                                      "frac": round(fma_us / dom["us"], 4)}
         # DRAM bytes per launch of that kernel from the committed ncu capture, if any
         tpath = os.path.join(ROOT, "profiles", "traffic.json")
         if os.path.exists(tpath):
@@ -708,6 +720,18 @@ def launch_floor_us(L, reps=200):
     b.record()
     torch.cuda.synchronize()
     return a.elapsed_time(b) * 1e3 / (reps // 50 * 50)
+
+
+def mixed_fma_rate(L, dev):
+    """Issue rate of fma.rn.f32.bf16 (three distinct register operands), warp instructions per ns per SM."""
+    import ctypes
+    from ddfnet_b200 import _lib
+    nbytes = int(L.ddf_b200_rate_probe_bytes())
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    v = ctypes.c_double(0.0)
+    _lib.check(L.ddf_b200_rate_probe(2, scratch.data_ptr(), nbytes, 1024, ctypes.byref(v),
+                                     torch.cuda.current_stream().cuda_stream))
+    return round(v.value, 3)
 
 
 def run_probe(args, rank, world, local_rank):
