@@ -13,7 +13,9 @@ Prints ONE JSON line.  `value` is algorithmic GB moved per second over the
 whole step with inputs resident in HBM, the step replayed from a CUDA graph and
 timed with CUDA events; `e2e` is the same sweep through `ddf_host_async` with pinned
 host buffers (host<->device copies inside the timed region); `roofline`
-describes the kernel instance that takes the largest share of the step;
+describes the kernel instance that takes the largest share of the step (against the
+HBM roof and, in `fma_issue_roof`, against the issue rate of the mixed-precision FMA that
+the library's probe kernel measures in the same run);
 `cpu_baseline` is the CPU oracle (a port of the reference's arithmetic: the
 reference has no CPU implementation) on a bounded sample.  With N > 1 every rank
 runs the same sweep on its own GPU (the op shards along the batch with no
