@@ -609,6 +609,71 @@ def run_sfnorm(args, rank, world, local_rank):
             "peak": peak, "peak_kind": f"of {peak_kind}", "per_shape": rows}))
 
 
+def run_nhwc(args, rank, world, local_rank):
+    """Per-layer sweep of the channels_last forward as the network harness calls it: raw 16-map
+    spatial-filter tensor, bias + FilterNorm + per-channel scale/shift + ReLU inside the kernel.
+    Bytes are the sweep's algorithmic bytes (9 filter maps); the kernel reads the 16-map tensor."""
+    from ddfnet_b200.nhwc import ddf_nhwc
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    peak, peak_kind = peaks()
+    rows = []
+    scale = 2.0 ** 0.5 / K
+    for mode in ("mul", "add"):
+        for (C, H, s) in SHAPES:
+            for dtname in ("bf16", "f16"):
+                dtype = {"bf16": torch.bfloat16, "f16": torch.float16}[dtname]
+                nb = algorithmic_bytes(BATCH, C, H, s, 2)
+                nsets = max(3, (2 * L2_BYTES) // nb + 2)
+                sets = []
+                for i in range(nsets):
+                    x, cf, sf = make_case(C, H, s, dtype, BATCH, dev, 700 + i)
+                    sf16 = torch.zeros(sf.shape[0], 16, sf.shape[2], sf.shape[3], dtype=dtype, device=dev)
+                    sf16[:, :K * K] = sf
+                    sets.append((x.contiguous(memory_format=torch.channels_last), cf,
+                                 sf16.contiguous(memory_format=torch.channels_last)))
+                bias = torch.zeros(K * K, dtype=torch.float32, device=dev)
+                osc = torch.ones(C, dtype=torch.float32, device=dev)
+                osh = torch.zeros(C, dtype=torch.float32, device=dev)
+
+                def fn(st):
+                    return ddf_nhwc(st[0], st[1], st[2], K, 1, s, mode, sf_bias=bias, sf_norm_scale=scale,
+                                    out_scale=osc, out_shift=osh, relu=True)
+                with torch.no_grad():
+                    for st in sets:
+                        fn(st)
+                    torch.cuda.synchronize()
+                    gr = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gr):
+                        for st in sets:
+                            fn(st)
+                    for _ in range(3):
+                        gr.replay()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    for _ in range(args.steps):
+                        gr.replay()
+                    b.record()
+                    torch.cuda.synchronize()
+                us = a.elapsed_time(b) * 1e3 / (args.steps * nsets)
+                rows.append({"C": C, "H": H, "stride": s, "dtype": dtname, "combine": mode, "bytes": nb,
+                             "us": round(us, 2), "gbs": round(nb / us / 1e3, 1),
+                             "frac": round(nb / us / 1e3 / peak, 4)})
+                del sets
+    tot_b = sum(r["bytes"] for r in rows)
+    tot_t = sum(r["us"] for r in rows)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "ddf_forward_nhwc_hbm_gbs", "value": round(tot_b / tot_t / 1e3, 1), "unit": "GB/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": 3, "ms_per_step": round(tot_t / 1e3, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16+f16 I/O, f32 arithmetic", "data": "synthetic",
+            "config": {"workload": "channels_last DDF forward with bias, FilterNorm, scale/shift and ReLU fused, "
+                                   "sweep shapes, mul and add, B=128",
+                       "l2": "rotating buffer sets larger than L2"},
+            "peak": peak, "peak_kind": f"of {peak_kind}", "per_shape": rows}))
+
+
 def measure_model(rank, world, local_rank, name, steps, warmup, channels_last=True, fold_bn="fused",
                   unfused_norm=False, no_graph=False):
     """Whole-network inference throughput (images/s) of the DDF-ResNet harness at the
@@ -848,7 +913,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="op", choices=["op", "model", "backward", "sfnorm", "probe"])
+    ap.add_argument("--workload", default="op", choices=["op", "model", "backward", "sfnorm", "nhwc", "probe"])
     ap.add_argument("--model", default="ddf_mul_resnet50", choices=sorted(MODEL_CFG))
     ap.add_argument("--quick", action="store_true",
                     help="op workload: skip the per-call timings and the CPU baseline (scaling runs)")
@@ -893,6 +958,8 @@ def main():
             run_backward(args, rank, world, local_rank)
         elif args.workload == "sfnorm":
             run_sfnorm(args, rank, world, local_rank)
+        elif args.workload == "nhwc":
+            run_nhwc(args, rank, world, local_rank)
         elif args.workload == "probe":
             run_probe(args, rank, world, local_rank)
         else:
